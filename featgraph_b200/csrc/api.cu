@@ -1,0 +1,64 @@
+// Error reporting, version and the host-only partitioning helpers of the C ABI.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace fg {
+
+std::string& last_error() {
+  static thread_local std::string msg;
+  return msg;
+}
+
+int fail(int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  last_error() = buf;
+  return code;
+}
+
+}  // namespace fg
+
+extern "C" const char* fg_last_error_string(void) { return fg::last_error().c_str(); }
+
+extern "C" const char* fg_version(void) { return "0.1.0"; }
+
+extern "C" int fg_shard_rows_by_nnz(const int32_t* indptr, int64_t n_rows, int32_t world,
+                                    int64_t* bounds) {
+  using namespace fg;
+  if (!indptr || !bounds) return fail(FG_ERR_INVALID_ARGUMENT, "null indptr or bounds");
+  if (n_rows < 0 || world <= 0)
+    return fail(FG_ERR_INVALID_ARGUMENT, "bad n_rows=%lld or world=%d", (long long)n_rows,
+                (int)world);
+  for (int64_t r = 0; r < n_rows; ++r)
+    if (indptr[r + 1] < indptr[r])
+      return fail(FG_ERR_INVALID_ARGUMENT, "indptr decreases at row %lld", (long long)r);
+  const int64_t nnz = n_rows > 0 ? (int64_t)indptr[n_rows] - indptr[0] : 0;
+  bounds[0] = 0;
+  for (int32_t k = 1; k < world; ++k) {
+    // First row boundary whose prefix count reaches k/world of the nonzeros,
+    // or the nearer of its two neighbours; never below the previous bound.
+    const int64_t target = indptr[0] + (nnz * k) / world;
+    const int32_t* it = std::lower_bound(indptr, indptr + n_rows + 1, (int32_t)target);
+    int64_t b = it - indptr;
+    if (b > 0 && b <= n_rows &&
+        (target - indptr[b - 1]) < ((int64_t)indptr[std::min(b, n_rows)] - target))
+      b = b - 1;
+    b = std::min<int64_t>(std::max<int64_t>(b, bounds[k - 1]), n_rows);
+    bounds[k] = b;
+  }
+  bounds[world] = n_rows;
+  return FG_OK;
+}
+
+extern "C" int fg_shard_edges(int64_t nnz, int32_t world, int64_t* bounds) {
+  using namespace fg;
+  if (!bounds) return fail(FG_ERR_INVALID_ARGUMENT, "null bounds");
+  if (nnz < 0 || world <= 0)
+    return fail(FG_ERR_INVALID_ARGUMENT, "bad nnz=%lld or world=%d", (long long)nnz, (int)world);
+  for (int32_t k = 0; k <= world; ++k) bounds[k] = (nnz * k) / world;
+  return FG_OK;
+}

@@ -1,0 +1,99 @@
+// Shared helpers of the featgraph_b200 kernels: error reporting, unfused fp32
+// arithmetic, cache-hinted loads/stores and cp.async wrappers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+
+#include "../../include/featgraph_b200.h"
+
+namespace fg {
+
+// ---- host side: per-thread error message -----------------------------------
+std::string& last_error();
+int fail(int code, const char* fmt, ...);
+
+#define FG_CUDA_TRY(expr)                                                      \
+  do {                                                                         \
+    cudaError_t fg_err__ = (expr);                                             \
+    if (fg_err__ != cudaSuccess)                                               \
+      return ::fg::fail(FG_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,           \
+                        cudaGetErrorString(fg_err__), __FILE__, __LINE__);     \
+  } while (0)
+
+// Switches the current device for the lifetime of the object.
+struct DeviceGuard {
+  int prev = -1;
+  bool changed = false;
+  cudaError_t status = cudaSuccess;
+  explicit DeviceGuard(int device) {
+    status = cudaGetDevice(&prev);
+    if (status == cudaSuccess && prev != device) {
+      status = cudaSetDevice(device);
+      changed = (status == cudaSuccess);
+    }
+  }
+  ~DeviceGuard() {
+    if (changed) cudaSetDevice(prev);
+  }
+};
+
+// ---- device side -------------------------------------------------------------
+#ifdef __CUDACC__
+
+// acc + a * b with the product rounded to fp32 before the sum: the arithmetic
+// of a code generator that does not contract into FMA.
+__device__ __forceinline__ float mul_then_add(float acc, float a, float b) {
+  return __fadd_rn(acc, __fmul_rn(a, b));
+}
+
+// Streaming (read-once) loads of the adjacency arrays.
+__device__ __forceinline__ int ld_stream(const int* p) { return __ldcs(p); }
+__device__ __forceinline__ float ld_stream(const float* p) { return __ldcs(p); }
+
+// Read-only gathers of feature rows.
+__device__ __forceinline__ float4 ld_gather4(const float* p) {
+  return __ldg(reinterpret_cast<const float4*>(p));
+}
+
+__device__ __forceinline__ void st_stream4(float* p, float4 v) {
+  __stcs(reinterpret_cast<float4*>(p), v);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// 16-byte asynchronous copy global -> shared that bypasses L1.
+__device__ __forceinline__ void cp_async16_cg(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+}
+// 16-byte asynchronous copy that allocates in L1 (reused rows hit there).
+__device__ __forceinline__ void cp_async16_ca(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+}
+// 4-byte asynchronous copy (no alignment beyond the element's own).
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+#endif  // __CUDACC__
+
+}  // namespace fg

@@ -1,0 +1,276 @@
+// COO SDDMM for sm_100a, single- and multi-head:
+//   out[e, h] = sum_{d<D} src[col[e], h*D+d] * dst[row[e], h*D+d]
+//
+// The sum over d runs in ascending order in one fp32 accumulator with the
+// product and the sum rounded separately -- the order of the reference's
+// unscheduled reduction (python/featgraph/op/vanilla_sddmm.py:43-47, 66-74) --
+// so results are bit-equal to a sequential loop.
+//
+// sddmm_tile_kernel: each warp owns 32 consecutive edges per tile.  The two
+// gathered feature rows of every edge are staged, 32 floats at a time, into
+// shared memory with 16-byte cp.async copies in which 8 lanes read one 128-byte
+// row segment (coalesced gathers); the copy of the next (tile, chunk) overlaps
+// the arithmetic of the current one.  Each lane then walks ITS edge's two
+// segments with float4 shared-memory loads (row pitch 36 floats, conflict
+// free) and adds the products in order.  COO lists sorted by row make
+// consecutive edges share dst[row], which then hits L1 (cp.async.ca).
+//
+// sddmm_generic_kernel: any shape / alignment, one thread per (edge, head).
+#include "common.cuh"
+
+namespace fg {
+
+constexpr int kSdChunk = 32;             // floats per row per stage
+constexpr int kSdPitch = kSdChunk + 4;   // smem row pitch (floats): conflict-free LDS.128
+constexpr int kSdWarps = 4;              // warps per CTA
+constexpr int kSdStageFloats = 2 * 32 * kSdPitch;  // src + dst rows of 32 edges
+constexpr int kSdWarpFloats = 2 * kSdStageFloats;  // double buffered
+constexpr int kSdSmemBytes = kSdWarps * kSdWarpFloats * 4;
+
+// HEADS_PER_CHUNK: number of heads that end inside one 32-float chunk
+// (1, 2, 4 or 8 <=> D = 32, 16, 8, 4), or 0 when D is a multiple of 32 larger
+// than 32 (heads end only at chunk boundaries).
+template <int HEADS_PER_CHUNK>
+__global__ void __launch_bounds__(kSdWarps * 32)
+sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
+                  const float* __restrict__ src, const float* __restrict__ dst,
+                  float* __restrict__ out, long long nnz, int F, int H, int tiles_per_warp) {
+  extern __shared__ __align__(16) float smem[];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  float* wbuf = smem + warp * kSdWarpFloats;
+
+  const long long n_tiles = (nnz + 31) / 32;
+  const long long tile0 = ((long long)blockIdx.x * kSdWarps + warp) * tiles_per_warp;
+  if (tile0 >= n_tiles) return;
+  const int my_tiles = (int)min((long long)tiles_per_warp, n_tiles - tile0);
+  const int n_chunks = F / kSdChunk;
+  const int total = my_tiles * n_chunks;
+  const int chunks_per_head = HEADS_PER_CHUNK == 0 ? (F / H) / kSdChunk : 1;
+
+  // Edge indices of the tile being issued (one edge per lane).
+  int r_iss = 0, c_iss = 0;
+  auto load_indices = [&](int t) {
+    const long long e = (tile0 + t) * 32 + lane;
+    r_iss = 0;
+    c_iss = 0;
+    if (t < my_tiles && e < nnz) {
+      r_iss = ld_stream(row + e);
+      c_iss = ld_stream(col + e);
+    }
+  };
+  // Stage `it` = (tile it / n_chunks, chunk it % n_chunks) into buffer it & 1.
+  auto issue = [&](int it) {
+    const int chunk = it % n_chunks;
+    if (chunk == 0) load_indices(it / n_chunks);
+    float* sbuf = wbuf + (it & 1) * kSdStageFloats;
+    float* dbuf = sbuf + 32 * kSdPitch;
+    const int part = (lane & 7) * 4;
+    const size_t foff = (size_t)chunk * kSdChunk + part;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int e = (lane >> 3) + 4 * k;
+      const int c = __shfl_sync(0xffffffffu, c_iss, e);
+      const int r = __shfl_sync(0xffffffffu, r_iss, e);
+      cp_async16_ca(sbuf + e * kSdPitch + part, src + (size_t)c * F + foff);
+      cp_async16_ca(dbuf + e * kSdPitch + part, dst + (size_t)r * F + foff);
+    }
+  };
+
+  issue(0);
+  cp_async_commit();
+  float acc = 0.f;
+  int head = 0;
+  for (int it = 0; it < total; ++it) {
+    if (it + 1 < total) issue(it + 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+
+    const int t = it / n_chunks;
+    const int chunk = it - t * n_chunks;
+    const long long e = (tile0 + t) * 32 + lane;
+    const float4* s4 = reinterpret_cast<const float4*>(wbuf + (it & 1) * kSdStageFloats +
+                                                       lane * kSdPitch);
+    const float4* d4 = reinterpret_cast<const float4*>(wbuf + (it & 1) * kSdStageFloats +
+                                                       (32 + lane) * kSdPitch);
+    if (chunk == 0) {
+      acc = 0.f;
+      head = 0;
+    }
+#pragma unroll
+    for (int q = 0; q < kSdChunk / 4; ++q) {
+      const float4 a = s4[q];
+      const float4 b = d4[q];
+      acc = mul_then_add(acc, a.x, b.x);
+      acc = mul_then_add(acc, a.y, b.y);
+      acc = mul_then_add(acc, a.z, b.z);
+      acc = mul_then_add(acc, a.w, b.w);
+      if (HEADS_PER_CHUNK > 0 && ((q + 1) % (8 / (HEADS_PER_CHUNK > 0 ? HEADS_PER_CHUNK : 1))) == 0) {
+        if (e < nnz) out[(size_t)e * H + head] = acc;
+        ++head;
+        acc = 0.f;
+      }
+    }
+    if (HEADS_PER_CHUNK == 0 && (chunk + 1) % chunks_per_head == 0) {
+      if (e < nnz) out[(size_t)e * H + head] = acc;
+      ++head;
+      acc = 0.f;
+    }
+    __syncwarp();  // every lane is done with this buffer before it is refilled
+  }
+  cp_async_wait<0>();
+}
+
+__global__ void __launch_bounds__(256)
+sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
+                     const float* __restrict__ src, const float* __restrict__ dst,
+                     float* __restrict__ out, long long n_out, int F, int H) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n_out) return;
+  const long long e = i / H;
+  const int h = (int)(i - e * H);
+  const int D = F / H;
+  const float* s = src + (size_t)col[e] * F + (size_t)h * D;
+  const float* d = dst + (size_t)row[e] * F + (size_t)h * D;
+  float acc = 0.f;
+  for (int k = 0; k < D; ++k) acc = mul_then_add(acc, s[k], d[k]);
+  out[i] = acc;
+}
+
+constexpr int kSdTilesPerWarp = 8;
+
+// 0 -> generic kernel; otherwise HEADS_PER_CHUNK + 1 of the tile kernel.
+static int sddmm_variant(int F, int H) {
+  if (F % kSdChunk != 0 || F % H != 0) return 0;
+  const int D = F / H;
+  if (D % kSdChunk == 0) return D == kSdChunk ? 2 : 1;  // hpc 1 or 0
+  if (D == 16) return 3;
+  if (D == 8) return 5;
+  if (D == 4) return 9;
+  return 0;
+}
+
+}  // namespace fg
+
+extern "C" int fg_sddmm_num_launches(int64_t nnz, int32_t feat_len, int32_t num_heads) {
+  (void)feat_len;
+  (void)num_heads;
+  return nnz > 0 ? 1 : 0;
+}
+
+extern "C" int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_heads, char* buf,
+                                 int64_t buf_len) {
+  using namespace fg;
+  if (!buf || buf_len <= 0) return fail(FG_ERR_INVALID_ARGUMENT, "null buffer");
+  if (num_heads <= 0 || feat_len <= 0 || feat_len % num_heads != 0)
+    return fail(FG_ERR_INVALID_ARGUMENT, "feat_len must be a positive multiple of num_heads");
+  const int v = sddmm_variant(feat_len, num_heads);
+  if (v == 0) {
+    snprintf(buf, (size_t)buf_len,
+             "sddmm_coo_f32 nnz=%lld feat_len=%d heads=%d | sddmm_generic_kernel grid=%lld x 256 thr",
+             (long long)nnz, feat_len, num_heads,
+             (long long)((nnz * num_heads + 255) / 256));
+  } else {
+    const long long tiles = (nnz + 31) / 32;
+    const long long per_cta = (long long)kSdWarps * kSdTilesPerWarp;
+    snprintf(buf, (size_t)buf_len,
+             "sddmm_coo_f32 nnz=%lld feat_len=%d heads=%d | sddmm_tile_kernel<heads_per_chunk=%d> "
+             "grid=%lld x %d thr, %d B smem, 32 edges x 32 floats per stage, double buffered",
+             (long long)nnz, feat_len, num_heads, v - 1, (long long)((tiles + per_cta - 1) / per_cta),
+             kSdWarps * 32, kSdSmemBytes);
+  }
+  return FG_OK;
+}
+
+extern "C" int fg_sddmm_coo_f32(const int32_t* row, const int32_t* col, const float* src,
+                                const float* dst, float* out, int64_t nnz, int64_t n_rows,
+                                int64_t n_cols, int32_t feat_len, int32_t num_heads,
+                                int32_t device, void* stream) {
+  using namespace fg;
+  if (nnz < 0 || n_rows < 0 || n_cols < 0 || feat_len <= 0 || num_heads <= 0)
+    return fail(FG_ERR_INVALID_ARGUMENT, "bad shape: nnz=%lld n_rows=%lld n_cols=%lld feat_len=%d heads=%d",
+                (long long)nnz, (long long)n_rows, (long long)n_cols, (int)feat_len, (int)num_heads);
+  if (feat_len % num_heads != 0)
+    return fail(FG_ERR_INVALID_ARGUMENT, "feat_len %d is not a multiple of num_heads %d",
+                (int)feat_len, (int)num_heads);
+  if (n_rows >= INT32_MAX || n_cols >= INT32_MAX)
+    return fail(FG_ERR_UNSUPPORTED, "row/column counts must fit int32");
+  if (nnz == 0) return FG_OK;
+  if (!row || !col || !src || !dst || !out)
+    return fail(FG_ERR_INVALID_ARGUMENT, "null device pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DeviceGuard guard(device);
+  if (guard.status != cudaSuccess)
+    return fail(FG_ERR_CUDA, "cannot select device %d: %s", device,
+                cudaGetErrorString(guard.status));
+
+  const bool aligned = (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
+                       (reinterpret_cast<uintptr_t>(dst) % 16 == 0);
+  const int variant = aligned ? sddmm_variant(feat_len, num_heads) : 0;
+  if (variant == 0) {
+    const long long n_out = (long long)nnz * num_heads;
+    const long long grid = (n_out + 255) / 256;
+    if (grid >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "output too large for the generic kernel");
+    sddmm_generic_kernel<<<(unsigned)grid, 256, 0, st>>>(row, col, src, dst, out, n_out, feat_len,
+                                                         num_heads);
+    FG_CUDA_TRY(cudaGetLastError());
+    return FG_OK;
+  }
+
+  const long long tiles = (nnz + 31) / 32;
+  const long long per_cta = (long long)kSdWarps * kSdTilesPerWarp;
+  const long long grid = (tiles + per_cta - 1) / per_cta;
+  if (grid >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "edge count too large");
+#define FG_SD_LAUNCH(HPC)                                                                    \
+  do {                                                                                       \
+    static thread_local int configured_dev = -1;                                             \
+    if (configured_dev != device) {                                                          \
+      FG_CUDA_TRY(cudaFuncSetAttribute(sddmm_tile_kernel<HPC>,                               \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                                       kSdSmemBytes));                                       \
+      configured_dev = device;                                                               \
+    }                                                                                        \
+    sddmm_tile_kernel<HPC><<<(unsigned)grid, kSdWarps * 32, kSdSmemBytes, st>>>(             \
+        row, col, src, dst, out, nnz, feat_len, num_heads, kSdTilesPerWarp);                 \
+  } while (0)
+  switch (variant - 1) {
+    case 0: FG_SD_LAUNCH(0); break;
+    case 1: FG_SD_LAUNCH(1); break;
+    case 2: FG_SD_LAUNCH(2); break;
+    case 4: FG_SD_LAUNCH(4); break;
+    default: FG_SD_LAUNCH(8); break;
+  }
+#undef FG_SD_LAUNCH
+  FG_CUDA_TRY(cudaGetLastError());
+  return FG_OK;
+}
+
+extern "C" int fg_sddmm_coo_f32_host(const int32_t* row, const int32_t* col,
+                                     const float* src_host, const float* dst_host,
+                                     float* out_host, float* src_stage, float* dst_stage,
+                                     float* out_stage, int64_t nnz, int64_t n_rows,
+                                     int64_t n_cols, int32_t feat_len, int32_t num_heads,
+                                     int32_t device, void* stream) {
+  using namespace fg;
+  if (!src_host || !dst_host || !out_host || !src_stage || !dst_stage || !out_stage)
+    return fail(FG_ERR_INVALID_ARGUMENT, "null host or staging buffer");
+  if (nnz < 0 || n_rows < 0 || n_cols < 0 || feat_len <= 0 || num_heads <= 0)
+    return fail(FG_ERR_INVALID_ARGUMENT, "bad shape");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DeviceGuard guard(device);
+  if (guard.status != cudaSuccess)
+    return fail(FG_ERR_CUDA, "cannot select device %d: %s", device,
+                cudaGetErrorString(guard.status));
+  const size_t sb = sizeof(float) * (size_t)n_cols * feat_len;
+  const size_t db = sizeof(float) * (size_t)n_rows * feat_len;
+  const size_t ob = sizeof(float) * (size_t)nnz * num_heads;
+  if (sb) FG_CUDA_TRY(cudaMemcpyAsync(src_stage, src_host, sb, cudaMemcpyHostToDevice, st));
+  if (db) FG_CUDA_TRY(cudaMemcpyAsync(dst_stage, dst_host, db, cudaMemcpyHostToDevice, st));
+  const int rc = fg_sddmm_coo_f32(row, col, src_stage, dst_stage, out_stage, nnz, n_rows, n_cols,
+                                  feat_len, num_heads, device, stream);
+  if (rc != FG_OK) return rc;
+  if (ob) FG_CUDA_TRY(cudaMemcpyAsync(out_host, out_stage, ob, cudaMemcpyDeviceToHost, st));
+  FG_CUDA_TRY(cudaStreamSynchronize(st));
+  return FG_OK;
+}

@@ -1,0 +1,219 @@
+"""SDDMM module classes with the interface of python/featgraph/module/sddmm.py.
+
+Single-head use is unchanged from the reference; ``compute_args={'num_heads': H}`` (or
+3-D placeholders (N, H, D)) selects the multi-head kernel, whose output is (nnz, H).
+"""
+import numpy as np
+import torch
+
+from .. import _lib
+from ..op import vanilla_sddmm, schedule_vanilla_sddmm_cuda_tree_reduce
+from ..op.spec import no_x86
+from ..runtime import Placeholder, array, cpu, gpu, zeros
+from ..util import util_partition_adj_coo_2d
+from .base import as_device_tensor, current_stream_handle, ptr, time_launches
+
+
+class SDDMMbase(object):
+    """Base of the SDDMM-like kernels (counterpart of SDDMMbase, sddmm.py:11-165).
+
+    Edges keep the order of the COO matrix given (sddmm.py:51-52); the adjacency values
+    are never read.
+    """
+
+    def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1):
+        coo = adj_scipy if adj_scipy.format == "coo" else adj_scipy.tocoo()
+        self._num_rows, self._num_cols = int(coo.shape[0]), int(coo.shape[1])
+        assert num_row_partitions >= 1, "num_row_partitions should be larger than or equal to 1"
+        assert num_col_partitions >= 1, "num_col_partitions should be larger than or equal to 1"
+        self._num_row_partitions = int(num_row_partitions)
+        self._num_col_partitions = int(num_col_partitions)
+        self._target = self._ctx = self._compute_func = self._schedule_func = None
+        self._register()
+
+        if self._num_row_partitions > 1 or self._num_col_partitions > 1:
+            # 2-D blocking; output position i holds edge edge_id_list[i], so sorting the
+            # ids gives the permutation back to the caller's order (sddmm.py:45-49).
+            edge_ids, rows, cols = self._preprocess_adj(coo, self._num_row_partitions,
+                                                        self._num_col_partitions)
+            self._edge_mapping = np.argsort(edge_ids)
+        else:
+            rows, cols = coo.row, coo.col
+        self._adj_row_indices = self._index_array(rows, "row indices")
+        self._adj_col_indices = self._index_array(cols, "col indices")
+        self._adj_row_indices_placeholder = Placeholder(self._adj_row_indices.shape, "int32",
+                                                        "adj_row_indices_placeholder")
+        self._adj_col_indices_placeholder = Placeholder(self._adj_col_indices.shape, "int32",
+                                                        "adj_col_indices_placeholder")
+        self._adj_row_indices_tvm = array(self._adj_row_indices, self._ctx)
+        self._adj_col_indices_tvm = array(self._adj_col_indices, self._ctx)
+        self._func = None
+        self._spec = None
+        self.out_tvm = None
+
+    @staticmethod
+    def _index_array(a, what):
+        if a.dtype == np.int32:
+            return np.ascontiguousarray(a)
+        if a.size and (a.max() > np.iinfo(np.int32).max or a.min() < 0):
+            raise ValueError("%s do not fit int32" % what)
+        return np.ascontiguousarray(a.astype(np.int32))
+
+    def _preprocess_adj(self, adj_scipy_coo, num_row_partitions=1, num_col_partitions=1):
+        return util_partition_adj_coo_2d(adj_scipy_coo, num_row_partitions, num_col_partitions)
+
+    def _register(self):
+        raise NotImplementedError("Please register target, ctx, compute_func, and schedule_func.")
+
+    def _specialise(self, input_placeholders, compute_args, schedule_args):
+        if self._target != "cuda":
+            raise no_x86(type(self).__name__ + ".build")
+        out = self._compute_func(*input_placeholders, self._adj_row_indices_placeholder,
+                                 self._adj_col_indices_placeholder, **compute_args)
+        sched = self._schedule_func(out, **schedule_args)
+        src, dst = input_placeholders[0], input_placeholders[1]
+        if src.shape[0] != self._num_cols:
+            raise ValueError("SrcFeat has %d rows, the adjacency has %d columns (SrcFeat is "
+                             "indexed by col)" % (src.shape[0], self._num_cols))
+        if dst.shape[0] != self._num_rows:
+            raise ValueError("DstFeat has %d rows, the adjacency has %d rows (DstFeat is "
+                             "indexed by row)" % (dst.shape[0], self._num_rows))
+        if src.dtype != "float32" or dst.dtype != "float32":
+            raise TypeError("only float32 features are supported")
+        return out, sched
+
+    def build(self, input_placeholders, compute_args, schedule_args):
+        """Fix the static shapes and allocate the zero-filled output.
+
+        input_placeholders : [SrcFeat (num_cols, F), DstFeat (num_rows, F)], or both 3-D
+            (N, H, D) for the multi-head kernel
+        compute_args : e.g. ``{'num_heads': H}``
+        schedule_args : e.g. ``{'num_cuda_blocks': n}`` (checked as in the reference, then
+            a hint only)
+        """
+        out, sched = self._specialise(input_placeholders, compute_args, schedule_args)
+        _lib.load()
+        self._spec, self._func = out, sched
+        self.out_tvm = zeros(out.shape, out.dtype, self._ctx)
+
+    def lower_to_ir(self, input_placeholders, compute_args, schedule_args):
+        """Debug text of the launch ``build`` would choose (sddmm.py:94-113)."""
+        import ctypes
+        out, sched = self._specialise(input_placeholders, compute_args, schedule_args)
+        buf = ctypes.create_string_buffer(2048)
+        _lib.check(_lib.load().fg_sddmm_describe(out.shape[0], out.attrs["feat_len"],
+                                                 out.attrs["num_heads"], buf, len(buf)))
+        return buf.value.decode() + " | hints: %r" % (sched.hints,)
+
+    def _launch(self, src, dst):
+        a = self._spec.attrs
+        _lib.check(_lib.load().fg_sddmm_coo_f32(
+            ptr(self._adj_row_indices_tvm.torch), ptr(self._adj_col_indices_tvm.torch),
+            ptr(src), ptr(dst), ptr(self.out_tvm.torch), self._adj_row_indices.shape[0],
+            self._num_rows, self._num_cols, a["feat_len"], a["num_heads"],
+            self._ctx.device_id, current_stream_handle(self._ctx)))
+
+    def _checked_inputs(self, input_tvm_ndarrays):
+        if self._spec is None:
+            raise RuntimeError("build() must be called before run()")
+        if len(input_tvm_ndarrays) != 2:
+            raise ValueError("SDDMM takes exactly two input arrays (SrcFeat, DstFeat)")
+        sp, dp = self._spec.inputs[0], self._spec.inputs[1]
+        src = as_device_tensor(input_tvm_ndarrays[0], self._ctx, sp.shape, sp.dtype, "SrcFeat")
+        dst = as_device_tensor(input_tvm_ndarrays[1], self._ctx, dp.shape, dp.dtype, "DstFeat")
+        return src, dst
+
+    def run(self, input_tvm_ndarrays):
+        """Launch with [SrcFeat (indexed by col), DstFeat (indexed by row)]; returns
+        ``self.out_tvm``, the same array every call (sddmm.py:115-129)."""
+        src, dst = self._checked_inputs(input_tvm_ndarrays)
+        self._launch(src, dst)
+        return self.out_tvm
+
+    def measure_average_time(self, input_tvm_ndarrays, num_runs):
+        """Mean kernel time in seconds over ``num_runs`` launches (sddmm.py:131-150)."""
+        src, dst = self._checked_inputs(input_tvm_ndarrays)
+        return time_launches(self._ctx, lambda: self._launch(src, dst), num_runs)
+
+    def run_host(self, src_host, dst_host, out_host):
+        """End-to-end call on HOST buffers (ideally pinned): uploads both feature arrays,
+        launches, downloads the result into ``out_host`` and synchronises; the edge lists
+        stay on the device.  Goes through the C ABI's fg_sddmm_coo_f32_host."""
+        if self._spec is None:
+            raise RuntimeError("build() must be called before run_host()")
+        sp_, dp_ = self._spec.inputs[0], self._spec.inputs[1]
+        for a, shape, what in ((src_host, sp_.shape, "src_host"), (dst_host, dp_.shape, "dst_host"),
+                               (out_host, self._spec.shape, "out_host")):
+            if not (isinstance(a, torch.Tensor) and a.device.type == "cpu" and a.is_contiguous()
+                    and a.dtype == torch.float32 and tuple(a.shape) == tuple(shape)):
+                raise ValueError("%s must be a contiguous float32 CPU tensor of shape %r"
+                                 % (what, tuple(shape)))
+        dev = self._ctx.torch_device
+        if getattr(self, "_stage", None) is None or tuple(self._stage[0].shape) != sp_.shape \
+                or tuple(self._stage[1].shape) != dp_.shape:
+            self._stage = (torch.empty(sp_.shape, dtype=torch.float32, device=dev),
+                           torch.empty(dp_.shape, dtype=torch.float32, device=dev))
+        a = self._spec.attrs
+        _lib.check(_lib.load().fg_sddmm_coo_f32_host(
+            ptr(self._adj_row_indices_tvm.torch), ptr(self._adj_col_indices_tvm.torch),
+            ptr(src_host), ptr(dst_host), ptr(out_host), ptr(self._stage[0]),
+            ptr(self._stage[1]), ptr(self.out_tvm.torch), self._adj_row_indices.shape[0],
+            self._num_rows, self._num_cols, a["feat_len"], a["num_heads"],
+            self._ctx.device_id, current_stream_handle(self._ctx)))
+        return out_host
+
+    def num_launches(self):
+        if self._spec is None:
+            return 0
+        a = self._spec.attrs
+        return int(_lib.load().fg_sddmm_num_launches(self._adj_row_indices.shape[0],
+                                                     a["feat_len"], a["num_heads"]))
+
+    @property
+    def edge_mapping(self):
+        assert self._target != "cuda", "no graph partitioning on cuda, no edge_mapping"
+        assert self._num_row_partitions > 1 or self._num_col_partitions > 1, \
+            "no graph partitioning, no edge_mapping"
+        return self._edge_mapping
+
+    @property
+    def ctx(self):
+        return self._ctx
+
+    @property
+    def target(self):
+        return self._target
+
+
+class VanillaSDDMMcuda(SDDMMbase):
+    """COO SDDMM on the GPU (counterpart of VanillaSDDMMcuda, sddmm.py:179-187);
+    ``device_id`` as in VanillaSpMMcuda."""
+
+    def __init__(self, adj_scipy, device_id=0):
+        self._device_id = int(device_id)
+        super(VanillaSDDMMcuda, self).__init__(adj_scipy, num_row_partitions=1,
+                                               num_col_partitions=1)
+
+    def _register(self):
+        if not torch.cuda.is_available():
+            raise RuntimeError("VanillaSDDMMcuda needs a CUDA device; there is no CPU fallback")
+        _lib.load()
+        self._target = "cuda"
+        self._ctx = gpu(self._device_id)
+        self._compute_func = vanilla_sddmm
+        self._schedule_func = schedule_vanilla_sddmm_cuda_tree_reduce
+
+
+class VanillaSDDMMx86(SDDMMbase):
+    """Name kept from the reference (sddmm.py:168-176).  The 2-D partitioning and
+    ``edge_mapping`` work, but this backend has no x86 code path: ``build`` raises
+    NotImplementedError."""
+
+    def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1):
+        super(VanillaSDDMMx86, self).__init__(adj_scipy, num_row_partitions, num_col_partitions)
+
+    def _register(self):
+        self._target = "llvm"
+        self._ctx = cpu(0)
+        self._compute_func = None
+        self._schedule_func = None

@@ -1,0 +1,59 @@
+"""SpMM op layer: same names and arguments as python/featgraph/op/vanilla_spmm.py."""
+from .spec import ComputeSpec, ScheduleSpec, no_x86
+
+
+def vanilla_spmm_csr_cuda(SrcFeat, Adj_indptr, Adj_indices, Adj_vals):
+    """Out[row, f] = sum over the row's nonzeros of Adj_vals[e] * SrcFeat[Adj_indices[e], f].
+
+    Counterpart of vanilla_spmm_csr_cuda (python/featgraph/op/vanilla_spmm.py:83-125).
+
+    SrcFeat : placeholder, (num_src_vertices, feat_len)
+    Adj_indptr : placeholder, (num_dst_vertices + 1,)
+    Adj_indices, Adj_vals : placeholders, (nnz,)
+    Returns the ComputeSpec of Out, (num_dst_vertices, feat_len).
+    """
+    assert Adj_indices.shape[0] == Adj_vals.shape[0]
+    if len(SrcFeat.shape) != 2:
+        raise ValueError("SrcFeat must be 2-D (num_src_vertices, feat_len), got %r"
+                         % (SrcFeat.shape,))
+    _, feat_len = SrcFeat.shape
+    num_dst_vertices = Adj_indptr.shape[0] - 1
+    return ComputeSpec("spmm_csr", (num_dst_vertices, feat_len), SrcFeat.dtype,
+                       (SrcFeat, Adj_indptr, Adj_indices, Adj_vals), {"feat_len": feat_len})
+
+
+def schedule_vanilla_spmm_csr_cuda(Out, num_cuda_blocks=None, num_threads_per_cuda_block=None):
+    """Counterpart of schedule_vanilla_spmm_csr_cuda (vanilla_spmm.py:128-146).
+
+    The reference binds rows to blockIdx.x and features to threadIdx.x with these two
+    knobs.  The kernels here pick their own launch shape from the degree distribution, so
+    the knobs are checked and recorded as hints only; the result does not depend on them.
+    """
+    num_rows, feat_len = Out.shape
+    if num_cuda_blocks is None:
+        num_cuda_blocks = num_rows
+    if num_threads_per_cuda_block is None:
+        num_threads_per_cuda_block = feat_len
+    if int(num_cuda_blocks) < 1 or int(num_threads_per_cuda_block) < 1:
+        raise ValueError("num_cuda_blocks and num_threads_per_cuda_block must be positive")
+    return ScheduleSpec(Out, "cuda", {"num_cuda_blocks": int(num_cuda_blocks),
+                                      "num_threads_per_cuda_block": int(num_threads_per_cuda_block)})
+
+
+def vanilla_spmm_csr_x86(SrcFeat, Adj_indptr, Adj_indices, Adj_vals, num_feat_partitions=1):
+    """x86 op of the reference (vanilla_spmm.py:6-62); not provided by this backend."""
+    raise no_x86("vanilla_spmm_csr_x86")
+
+
+def schedule_vanilla_spmm_csr_x86(Out):
+    raise no_x86("schedule_vanilla_spmm_csr_x86")
+
+
+def vanilla_spmm_dds_x86(SrcFeat, Adj_s1_pos, Adj_s1_idx, Adj_vals, d1_size, d2_size,
+                         num_feat_partitions=1):
+    """x86 DDS op of the reference (vanilla_spmm.py:149-220); not provided by this backend."""
+    raise no_x86("vanilla_spmm_dds_x86")
+
+
+def schedule_vanilla_spmm_dds_x86(Out):
+    raise no_x86("schedule_vanilla_spmm_dds_x86")

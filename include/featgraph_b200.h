@@ -1,0 +1,139 @@
+/*
+ * featgraph_b200 -- C ABI of the sm_100a SpMM / SDDMM backend.
+ *
+ * Every entry point returns an int status (FG_OK == 0) and never throws or
+ * aborts; fg_last_error_string() gives the message of the calling thread's
+ * last failure.  Pointers whose name ends in _dev are device pointers on the
+ * device the call (or the plan) names, pointers ending in _host are ordinary
+ * host memory.  `stream` is a cudaStream_t passed as void* (NULL = the legacy
+ * default stream).  No torch types appear in any signature.
+ *
+ * Each declaration cites the interface of the reference implementation
+ * (amazon-science/FeatGraph, paths relative to that project) that it stands
+ * in for.
+ */
+#ifndef FEATGRAPH_B200_H_
+#define FEATGRAPH_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum fg_status {
+  FG_OK = 0,
+  FG_ERR_INVALID_ARGUMENT = 1, /* bad shape, null pointer, inconsistent indptr */
+  FG_ERR_CUDA = 2,             /* a CUDA runtime call failed                 */
+  FG_ERR_UNSUPPORTED = 3,      /* size beyond what the ABI can index         */
+  FG_ERR_OUT_OF_MEMORY = 4
+};
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* fg_last_error_string(void);
+
+/* Library version, "major.minor.patch". */
+const char* fg_version(void);
+
+/* ------------------------------------------------------------------ SpMM -- */
+
+/* Opaque launch plan of one CSR matrix: rows binned by degree (a light list
+ * served by sub-warp groups, a heavy list served by staged single-warp CTAs),
+ * the feature-slab width chosen from the device's L2 size, an auxiliary
+ * stream and two events used to overlap the heavy and the light kernel. */
+typedef struct fg_spmm_plan fg_spmm_plan;
+
+/* Builds the plan from the HOST copy of indptr (n_rows + 1 int32 entries).
+ * Stands in for the specialisation step of SpMMbase.build
+ * (python/featgraph/module/spmm.py:81-111) together with the schedule
+ * schedule_vanilla_spmm_csr_cuda (python/featgraph/op/vanilla_spmm.py:128-146).
+ * heavy_threshold <= 0 selects the built-in default. */
+int fg_spmm_plan_create(const int32_t* indptr_host, int64_t n_rows,
+                        int64_t n_cols, int32_t feat_len, int32_t device,
+                        int32_t heavy_threshold, fg_spmm_plan** out_plan);
+
+int fg_spmm_plan_destroy(fg_spmm_plan* plan);
+
+/* Writes a one-line human readable description of the plan (bins, slab width,
+ * launch shapes) into buf.  Stands in for SpMMbase.lower_to_ir
+ * (python/featgraph/module/spmm.py:113-140). */
+int fg_spmm_plan_describe(const fg_spmm_plan* plan, char* buf, int64_t buf_len);
+
+/* Number of kernels one fg_spmm_csr_f32 call launches with this plan. */
+int fg_spmm_plan_num_launches(const fg_spmm_plan* plan);
+
+/* Y[r, f] = sum over e in [indptr[r], indptr[r+1]) of vals[e] * X[indices[e], f],
+ * e ascending, one fp32 accumulator per (r, f), product and sum rounded
+ * separately.  X is (n_cols, feat_len) row-major, Y is (n_rows, feat_len)
+ * row-major and every element of Y is overwritten.  Stands in for the
+ * compiled function that SpMMbase.run calls
+ * (python/featgraph/module/spmm.py:142-161), i.e. vanilla_spmm_csr_cuda
+ * (python/featgraph/op/vanilla_spmm.py:83-125). */
+int fg_spmm_csr_f32(const fg_spmm_plan* plan, const int32_t* indptr_dev,
+                    const int32_t* indices_dev, const float* vals_dev,
+                    const float* x_dev, float* y_dev, void* stream);
+
+/* Same computation from HOST buffers: uploads X, launches, downloads Y and
+ * synchronises the stream.  The adjacency stays resident on the device, as it
+ * does in the reference after SpMMbase.__init__
+ * (python/featgraph/module/spmm.py:67-69); x_stage_dev / y_stage_dev are
+ * caller-provided device buffers of the sizes of X and Y. */
+int fg_spmm_csr_f32_host(const fg_spmm_plan* plan, const int32_t* indptr_dev,
+                         const int32_t* indices_dev, const float* vals_dev,
+                         const float* x_host, float* y_host,
+                         float* x_stage_dev, float* y_stage_dev, void* stream);
+
+/* ----------------------------------------------------------------- SDDMM -- */
+
+/* out[e, h] = sum over d < D of src[col[e], h*D + d] * dst[row[e], h*D + d],
+ * d ascending, one fp32 accumulator per (e, h), product and sum rounded
+ * separately; D = feat_len / num_heads.  src is (n_cols, feat_len) row-major
+ * and is indexed by COL, dst is (n_rows, feat_len) row-major and is indexed
+ * by ROW; out is (nnz, num_heads) row-major in the given edge order.
+ * num_heads == 1 is the reference's vanilla_sddmm
+ * (python/featgraph/op/vanilla_sddmm.py:6-63) as run by SDDMMbase.run
+ * (python/featgraph/module/sddmm.py:115-129); num_heads > 1 is the multi-head
+ * extension, which has no counterpart in the reference. */
+int fg_sddmm_coo_f32(const int32_t* row_dev, const int32_t* col_dev,
+                     const float* src_dev, const float* dst_dev, float* out_dev,
+                     int64_t nnz, int64_t n_rows, int64_t n_cols,
+                     int32_t feat_len, int32_t num_heads, int32_t device,
+                     void* stream);
+
+/* Same computation from HOST feature buffers (edge lists stay resident, as in
+ * SDDMMbase.__init__, python/featgraph/module/sddmm.py:59-60). */
+int fg_sddmm_coo_f32_host(const int32_t* row_dev, const int32_t* col_dev,
+                          const float* src_host, const float* dst_host,
+                          float* out_host, float* src_stage_dev,
+                          float* dst_stage_dev, float* out_stage_dev,
+                          int64_t nnz, int64_t n_rows, int64_t n_cols,
+                          int32_t feat_len, int32_t num_heads, int32_t device,
+                          void* stream);
+
+/* Number of kernels one fg_sddmm_coo_f32 call launches for this shape. */
+int fg_sddmm_num_launches(int64_t nnz, int32_t feat_len, int32_t num_heads);
+
+/* One-line description of the launch chosen for this shape; stands in for
+ * SDDMMbase.lower_to_ir (python/featgraph/module/sddmm.py:94-113). */
+int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_heads,
+                      char* buf, int64_t buf_len);
+
+/* ------------------------------------------------- multi-GPU partitioning -- */
+
+/* Splits the rows of a CSR matrix into `world` contiguous blocks holding about
+ * nnz / world nonzeros each; a row is never split.  bounds receives world + 1
+ * row indices, bounds[0] = 0, bounds[world] = n_rows.  Pure host code.  The
+ * reference is single-device (python/featgraph/module/spmm.py:218), so this
+ * has no counterpart there. */
+int fg_shard_rows_by_nnz(const int32_t* indptr_host, int64_t n_rows,
+                         int32_t world, int64_t* bounds);
+
+/* Splits nnz edges into `world` contiguous, near-equal ranges (world + 1
+ * bounds).  Pure host code; no counterpart in the reference
+ * (python/featgraph/module/sddmm.py:185 is single-device). */
+int fg_shard_edges(int64_t nnz, int32_t world, int64_t* bounds);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FEATGRAPH_B200_H_ */

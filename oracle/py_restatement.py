@@ -1,0 +1,35 @@
+"""Pure-Python restatement of the same loops, for tiny cases only.
+
+TEST INFRASTRUCTURE.  A second, independent spelling of the summation order
+documented in fg_oracle.c (np.float32 scalars, one operation at a time) that
+the tests use to check the C oracle bit for bit.
+"""
+import numpy as np
+
+
+def spmm_csr(indptr, indices, vals, x):
+    """vanilla_spmm.py:46-56 with the loop order of :73 -- e ascending per row."""
+    n_rows, f = len(indptr) - 1, x.shape[1]
+    y = np.zeros((n_rows, f), np.float32)
+    for r in range(n_rows):
+        for e in range(indptr[r], indptr[r + 1]):
+            v = np.float32(vals[e])
+            for k in range(f):
+                prod = np.float32(v * np.float32(x[indices[e], k]))
+                y[r, k] = np.float32(y[r, k] + prod)
+    return y
+
+
+def sddmm_coo(row, col, src, dst, num_heads=1):
+    """vanilla_sddmm.py:43-47 -- k ascending per edge (per head)."""
+    nnz, f = len(row), src.shape[1]
+    d = f // num_heads
+    out = np.zeros((nnz, num_heads), np.float32)
+    for e in range(nnz):
+        for h in range(num_heads):
+            acc = np.float32(0.0)
+            for k in range(h * d, (h + 1) * d):
+                prod = np.float32(np.float32(src[col[e], k]) * np.float32(dst[row[e], k]))
+                acc = np.float32(acc + prod)
+            out[e, h] = acc
+    return out.reshape(nnz) if num_heads == 1 else out

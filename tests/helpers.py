@@ -1,0 +1,26 @@
+"""Small seeded input builders shared by the tests."""
+import numpy as np
+import scipy.sparse as sp
+
+
+def random_csr(n_rows, n_cols, density, seed, empty_rows=(), dense_rows=()):
+    rs = np.random.RandomState(seed)
+    a = sp.random(n_rows, n_cols, density=density, format="lil", random_state=rs,
+                  dtype=np.float32)
+    for r in dense_rows:
+        a[r, :] = rs.random_sample(n_cols).astype(np.float32) + 0.5
+    for r in empty_rows:
+        a[r, :] = 0
+    a = a.tocsr().astype(np.float32)
+    a.eliminate_zeros()
+    a.sort_indices()
+    return a
+
+
+def features(shape, seed):
+    return np.random.default_rng(seed).standard_normal(shape, dtype=np.float32)
+
+
+def bits(a):
+    """View float32 results as int32 so that comparisons are bit-exact (and NaN-safe)."""
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.int32)

@@ -34,7 +34,7 @@ def schedule_vanilla_spmm_csr_cuda(Out, num_cuda_blocks=None, num_threads_per_cu
         num_cuda_blocks = num_rows
     if num_threads_per_cuda_block is None:
         num_threads_per_cuda_block = feat_len
-    if int(num_cuda_blocks) < 1 or int(num_threads_per_cuda_block) < 1:
+    if num_rows > 0 and (int(num_cuda_blocks) < 1 or int(num_threads_per_cuda_block) < 1):
         raise ValueError("num_cuda_blocks and num_threads_per_cuda_block must be positive")
     return ScheduleSpec(Out, "cuda", {"num_cuda_blocks": int(num_cuda_blocks),
                                       "num_threads_per_cuda_block": int(num_threads_per_cuda_block)})

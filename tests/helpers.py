@@ -22,5 +22,10 @@ def features(shape, seed):
 
 
 def bits(a):
-    """View float32 results as int32 so that comparisons are bit-exact (and NaN-safe)."""
-    return np.ascontiguousarray(a, dtype=np.float32).view(np.int32)
+    """float32 results as int32 bit patterns, so that comparisons are bit-exact.  NaNs are
+    mapped to one pattern: the payload of a propagated NaN differs between x86 (keeps the
+    operand's) and the GPU (canonical NaN) and carries no information."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    out = a.view(np.int32).copy()
+    out[np.isnan(a)] = 0x7FC00000
+    return out

@@ -83,6 +83,31 @@ int fg_spmm_csr_f32_host(const fg_spmm_plan* plan, const int32_t* indptr_dev,
                          const float* x_host, float* y_host,
                          float* x_stage_dev, float* y_stage_dev, void* stream);
 
+/* The same SpMM for callers that must not allocate device memory (a plug-in
+ * inside a server that owns the whole device pool, a loop in which cudaMalloc
+ * and cudaFree are banned after start-up because they synchronise the device,
+ * a process whose memory budget is already spent).  It has no counterpart in
+ * the reference.  No plan is needed and nothing is allocated, by this library
+ * or by any library it calls: the degree-ordered row list lives in a fixed
+ * array inside the library image, sized for fg_spmm_noalloc_max_rows() rows
+ * (1 048 576; about 4 MiB held by every GPU that loads the library until the
+ * process exits) and rebuilt on the device by every call.  More rows than that,
+ * feat_len not a multiple of 32, or x_dev / y_dev not 16-byte aligned return
+ * FG_ERR_UNSUPPORTED with a message.  The first call on a device looks up the
+ * array's device address; make that call before starting any stream capture.
+ * All calls share the one array, so two calls that overlap on the same GPU
+ * (different streams or threads) race; issue them one after the other.  Long
+ * rows take the same group-per-row kernel as short ones, so graphs with very
+ * long rows run slower here than through a plan.  Results are bit-identical to
+ * fg_spmm_csr_f32. */
+int fg_spmm_csr_f32_noalloc(const int32_t* indptr_dev, const int32_t* indices_dev,
+                            const float* vals_dev, const float* x_dev, float* y_dev,
+                            int64_t n_rows, int64_t n_cols, int32_t feat_len,
+                            int32_t device, void* stream);
+
+/* Largest n_rows fg_spmm_csr_f32_noalloc accepts. */
+int fg_spmm_noalloc_max_rows(void);
+
 /* ----------------------------------------------------------------- SDDMM -- */
 
 /* out[e, h] = sum over d < D of src[col[e], h*D + d] * dst[row[e], h*D + d],

@@ -51,6 +51,15 @@ __device__ __forceinline__ float mul_then_add(float acc, float a, float b) {
   return __fadd_rn(acc, __fmul_rn(a, b));
 }
 
+// The same for two adjacent features: scalar products, one packed fp32x2 add
+// (Blackwell's add.f32x2).  The products are deliberately NOT a packed
+// mul.f32x2: ptxas 12.9 contracts a single-use packed multiply feeding a packed
+// add into a packed FMA even though both carry .rn (measured: 20 % of random
+// results differ from the unfused ones), which would break bit-parity.
+__device__ __forceinline__ float2 mul_then_add2(float2 acc, float a, float2 b) {
+  return __fadd2_rn(acc, make_float2(__fmul_rn(a, b.x), __fmul_rn(a, b.y)));
+}
+
 // Streaming (read-once) loads of the adjacency arrays.
 __device__ __forceinline__ int ld_stream(const int* p) { return __ldcs(p); }
 __device__ __forceinline__ float ld_stream(const float* p) { return __ldcs(p); }

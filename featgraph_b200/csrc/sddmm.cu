@@ -12,8 +12,9 @@
 // row segment (coalesced gathers); the copy of the next (tile, chunk) overlaps
 // the arithmetic of the current one.  Each lane then walks ITS edge's two
 // segments with float4 shared-memory loads (row pitch 36 floats, conflict
-// free) and adds the products in order.  COO lists sorted by row make
-// consecutive edges share dst[row], which then hits L1 (cp.async.ca).
+// free) and adds the products in order.  Runs of consecutive edges with the
+// same row (the normal case for a row-sorted COO list) stage dst[row] once per
+// run and read it back as a broadcast.
 //
 // sddmm_generic_kernel: any shape / alignment, one thread per (edge, head).
 #include "common.cuh"
@@ -23,7 +24,8 @@ namespace fg {
 constexpr int kSdChunk = 32;             // floats per row per stage
 constexpr int kSdPitch = kSdChunk + 4;   // smem row pitch (floats): conflict-free LDS.128
 constexpr int kSdWarps = 4;              // warps per CTA
-constexpr int kSdStageFloats = 2 * 32 * kSdPitch;  // src + dst rows of 32 edges
+// one stage: src segments of 32 edges, dst segments of up to 32 distinct rows, 32 slot ids
+constexpr int kSdStageFloats = 2 * 32 * kSdPitch + 32;
 constexpr int kSdWarpFloats = 2 * kSdStageFloats;  // double buffered
 constexpr int kSdSmemBytes = kSdWarps * kSdWarpFloats * 4;
 
@@ -35,6 +37,7 @@ __global__ void __launch_bounds__(kSdWarps * 32)
 sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
                   const float* __restrict__ src, const float* __restrict__ dst,
                   float* __restrict__ out, long long nnz, int F, int H, int tiles_per_warp) {
+  constexpr unsigned kFull = 0xffffffffu;
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -48,56 +51,76 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
   const int total = my_tiles * n_chunks;
   const int chunks_per_head = HEADS_PER_CHUNK == 0 ? (F / H) / kSdChunk : 1;
 
-  // Edge indices of the tile being issued (one edge per lane).
-  int r_iss = 0, c_iss = 0;
-  auto load_indices = [&](int t) {
+  // State of the tile being issued: one edge per lane, and the tile's runs of
+  // equal row index.  Edge lists sorted by row repeat dst[row] for hundreds of
+  // consecutive edges; each distinct run is staged once ("slot") and the lanes of
+  // the run read it back as a shared-memory broadcast.
+  int r_iss = 0, c_iss = 0, slot_iss = 0, n_slots = 1;
+  unsigned run_heads = 1u;
+  // Indices of the tile after the one being issued, fetched a whole tile ahead
+  // so that their DRAM latency never stalls the copy pipeline.
+  int r_ahead = 0, c_ahead = 0;
+  auto fetch_indices = [&](int t) {
     const long long e = (tile0 + t) * 32 + lane;
-    r_iss = 0;
-    c_iss = 0;
+    r_ahead = 0;
+    c_ahead = 0;
     if (t < my_tiles && e < nnz) {
-      r_iss = ld_stream(row + e);
-      c_iss = ld_stream(col + e);
+      r_ahead = ld_stream(row + e);
+      c_ahead = ld_stream(col + e);
     }
   };
-  // Stage `it` = (tile it / n_chunks, chunk it % n_chunks) into buffer it & 1.
-  auto issue = [&](int it) {
-    const int chunk = it % n_chunks;
-    if (chunk == 0) load_indices(it / n_chunks);
-    float* sbuf = wbuf + (it & 1) * kSdStageFloats;
+  auto begin_tile = [&](int t) {
+    r_iss = r_ahead;
+    c_iss = c_ahead;
+    fetch_indices(t + 1);
+    const int r_left = __shfl_up_sync(kFull, r_iss, 1);
+    run_heads = __ballot_sync(kFull, lane == 0 || r_iss != r_left);
+    slot_iss = __popc(run_heads & (0xffffffffu >> (31 - lane))) - 1;
+    n_slots = __popc(run_heads);
+  };
+  // Stage (tile t_iss, chunk ch_iss) into buffer `buf`.
+  int t_iss = 0, ch_iss = 0;
+  auto issue = [&](int buf) {
+    if (ch_iss == 0) begin_tile(t_iss);
+    float* sbuf = wbuf + buf * kSdStageFloats;
     float* dbuf = sbuf + 32 * kSdPitch;
+    reinterpret_cast<int*>(dbuf + 32 * kSdPitch)[lane] = slot_iss;
     const int part = (lane & 7) * 4;
-    const size_t foff = (size_t)chunk * kSdChunk + part;
+    const size_t foff = (size_t)ch_iss * kSdChunk + part;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const int e = (lane >> 3) + 4 * k;
-      const int c = __shfl_sync(0xffffffffu, c_iss, e);
-      const int r = __shfl_sync(0xffffffffu, r_iss, e);
-      cp_async16_ca(sbuf + e * kSdPitch + part, src + (size_t)c * F + foff);
-      cp_async16_ca(dbuf + e * kSdPitch + part, dst + (size_t)r * F + foff);
+      const int c = __shfl_sync(kFull, c_iss, e);
+      cp_async16_cg(sbuf + e * kSdPitch + part, src + (size_t)c * F + foff);
+    }
+    for (int k = 0; 4 * k < n_slots; ++k) {
+      const int slot = (lane >> 3) + 4 * k;
+      const unsigned head = __fns(run_heads, 0, min(slot, n_slots - 1) + 1);
+      const int r = __shfl_sync(kFull, r_iss, head);
+      if (slot < n_slots) cp_async16_ca(dbuf + slot * kSdPitch + part, dst + (size_t)r * F + foff);
+    }
+    if (++ch_iss == n_chunks) {
+      ch_iss = 0;
+      ++t_iss;
     }
   };
 
+  fetch_indices(0);
   issue(0);
   cp_async_commit();
   float acc = 0.f;
-  int head = 0;
+  int head = 0, chunk = 0;
+  long long e = tile0 * 32 + lane;
   for (int it = 0; it < total; ++it) {
-    if (it + 1 < total) issue(it + 1);
+    if (it + 1 < total) issue((it + 1) & 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncwarp();
 
-    const int t = it / n_chunks;
-    const int chunk = it - t * n_chunks;
-    const long long e = (tile0 + t) * 32 + lane;
-    const float4* s4 = reinterpret_cast<const float4*>(wbuf + (it & 1) * kSdStageFloats +
-                                                       lane * kSdPitch);
-    const float4* d4 = reinterpret_cast<const float4*>(wbuf + (it & 1) * kSdStageFloats +
-                                                       (32 + lane) * kSdPitch);
-    if (chunk == 0) {
-      acc = 0.f;
-      head = 0;
-    }
+    const float* stage = wbuf + (it & 1) * kSdStageFloats;
+    const int slot = reinterpret_cast<const int*>(stage + 64 * kSdPitch)[lane];
+    const float4* s4 = reinterpret_cast<const float4*>(stage + lane * kSdPitch);
+    const float4* d4 = reinterpret_cast<const float4*>(stage + (32 + slot) * kSdPitch);
 #pragma unroll
     for (int q = 0; q < kSdChunk / 4; ++q) {
       const float4 a = s4[q];
@@ -112,10 +135,17 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
         acc = 0.f;
       }
     }
-    if (HEADS_PER_CHUNK == 0 && (chunk + 1) % chunks_per_head == 0) {
+    ++chunk;
+    if (HEADS_PER_CHUNK == 0 && chunk % chunks_per_head == 0) {
       if (e < nnz) out[(size_t)e * H + head] = acc;
       ++head;
       acc = 0.f;
+    }
+    if (chunk == n_chunks) {  // next stage belongs to the next tile
+      chunk = 0;
+      head = 0;
+      acc = 0.f;
+      e += 32;
     }
     __syncwarp();  // every lane is done with this buffer before it is refilled
   }

@@ -50,95 +50,137 @@ spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   }
   const size_t col_off = (size_t)slab * (4 * G) + (size_t)gl * 4;
   const float* xcol = X + col_off;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float2 acc_lo = make_float2(0.f, 0.f), acc_hi = make_float2(0.f, 0.f);
+
+  // Index/value tile of the NEXT iteration, fetched one iteration ahead so that
+  // its DRAM latency overlaps the gathers of the current one.
+  int idx_next = 0;
+  float v_next = 0.f;
+  if (gl < end - e) {
+    idx_next = ld_stream(indices + e + gl);
+    v_next = ld_stream(vals + e + gl);
+  }
 
   // The loop is warp-uniform: groups whose row is exhausted idle (cnt <= 0).
   while (__any_sync(kFull, e < end)) {
     const int cnt = end - e;
-    int idx = 0;
-    float v = 0.f;
-    if (gl < cnt) {
-      idx = ld_stream(indices + e + gl);
-      v = ld_stream(vals + e + gl);
+    const int idx = idx_next;
+    const float v = v_next;
+    idx_next = 0;
+    v_next = 0.f;
+    if (gl < cnt - G) {
+      idx_next = ld_stream(indices + e + G + gl);
+      v_next = ld_stream(vals + e + G + gl);
     }
 #pragma unroll
     for (int j0 = 0; j0 < G; j0 += 8) {
-      if (j0 > 0 && !__any_sync(kFull, j0 < cnt)) break;
       float4 x[8];
-      float vv[8];
+      if (__all_sync(kFull, cnt >= j0 + 8)) {
+        // every group of the warp has a full batch: no predicates
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int c = __shfl_sync(kFull, idx, j0 + u, G);
-        vv[u] = __shfl_sync(kFull, v, j0 + u, G);
-        if (j0 + u < cnt) x[u] = ld_gather4(xcol + (size_t)c * F);
-      }
+        for (int u = 0; u < 8; ++u) {
+          const int c = __shfl_sync(kFull, idx, j0 + u, G);
+          x[u] = ld_gather4(xcol + (size_t)c * F);
+        }
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (j0 + u < cnt) {
-          acc.x = mul_then_add(acc.x, vv[u], x[u].x);
-          acc.y = mul_then_add(acc.y, vv[u], x[u].y);
-          acc.z = mul_then_add(acc.z, vv[u], x[u].z);
-          acc.w = mul_then_add(acc.w, vv[u], x[u].w);
+        for (int u = 0; u < 8; ++u) {
+          const float vu = __shfl_sync(kFull, v, j0 + u, G);
+          acc_lo = mul_then_add2(acc_lo, vu, make_float2(x[u].x, x[u].y));
+          acc_hi = mul_then_add2(acc_hi, vu, make_float2(x[u].z, x[u].w));
+        }
+      } else {
+        if (!__any_sync(kFull, j0 < cnt)) break;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int c = __shfl_sync(kFull, idx, j0 + u, G);
+          if (j0 + u < cnt) x[u] = ld_gather4(xcol + (size_t)c * F);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float vu = __shfl_sync(kFull, v, j0 + u, G);
+          if (j0 + u < cnt) {
+            acc_lo = mul_then_add2(acc_lo, vu, make_float2(x[u].x, x[u].y));
+            acc_hi = mul_then_add2(acc_hi, vu, make_float2(x[u].z, x[u].w));
+          }
         }
       }
     }
     if (cnt > 0) e += (cnt < G ? cnt : G);
   }
-  if (valid) st_stream4(Y + (size_t)row * F + col_off, acc);
+  if (valid)
+    st_stream4(Y + (size_t)row * F + col_off, make_float4(acc_lo.x, acc_lo.y, acc_hi.x, acc_hi.y));
 }
 
-constexpr int kHvEdges = 32;              // edges per stage
-constexpr int kHvDist = 5;                // stages of gathers in flight
-constexpr int kHvXSlots = kHvDist + 1;    // ring of gathered X segments
-constexpr int kHvISlots = 2 * kHvDist + 1;  // ring of index/value tiles
+constexpr int kHvEdges = 32;    // nonzeros per stage
+constexpr int kHvXSlots = 8;    // ring of gathered X segments (power of two)
+constexpr int kHvDist = kHvXSlots - 1;  // stages of gathers in flight
+constexpr int kHvISlots = 16;   // ring of index/value tiles, >= 2 * kHvDist + 1
 
-// One warp per (heavy row, 32-float slab).
+template <int VEC>
+constexpr int heavy_smem_bytes() {
+  return kHvXSlots * kHvEdges * 32 * VEC * 4 + kHvISlots * kHvEdges * 8;
+}
+
+// One warp per (heavy row, 32*VEC-float slab); VEC = floats per lane (1 or 2).
+template <int VEC>
 __global__ void __launch_bounds__(32)
 spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
                   float* __restrict__ Y, const int* __restrict__ rows, int n_listed,
                   int subs_per_slab, int F) {
-  __shared__ __align__(16) float xs[kHvXSlots][kHvEdges][32];
-  __shared__ __align__(16) int idx_s[kHvISlots][kHvEdges];
-  __shared__ __align__(16) float val_s[kHvISlots][kHvEdges];
+  constexpr int kSlab = 32 * VEC;                 // floats per gathered segment
+  constexpr int kLanesPerRow = kSlab / 4;         // 16-byte copies per segment
+  constexpr int kRowsPerCopy = 32 / kLanesPerRow; // segments covered by one warp-wide copy
+  extern __shared__ __align__(16) unsigned char heavy_smem[];
+  float(*xs)[kHvEdges][kSlab] = reinterpret_cast<float(*)[kHvEdges][kSlab]>(heavy_smem);
+  int(*idx_s)[kHvEdges] =
+      reinterpret_cast<int(*)[kHvEdges]>(heavy_smem + kHvXSlots * kHvEdges * kSlab * 4);
+  float(*val_s)[kHvEdges] = reinterpret_cast<float(*)[kHvEdges]>(
+      heavy_smem + kHvXSlots * kHvEdges * kSlab * 4 + kHvISlots * kHvEdges * 4);
 
   const int lane = threadIdx.x;
-  // Item order: (residency slab, row, 32-float sub-slab) so that the sub-slabs
-  // of one row run side by side and share their index stream in L2.
+  // Item order: (residency slab, row, sub-slab) so that the sub-slabs of one
+  // row run side by side and share their index stream in L2.
   const long long item = blockIdx.x;
   const long long per_slab = (long long)n_listed * subs_per_slab;
   const int ss = (int)(item / per_slab);
   const long long rem = item - ss * per_slab;
   const int row = __ldg(rows + rem / subs_per_slab);
-  const int slab32 = ss * subs_per_slab + (int)(rem % subs_per_slab);
+  const int sub = ss * subs_per_slab + (int)(rem % subs_per_slab);
 
   const int beg = __ldg(indptr + row);
   const int deg = __ldg(indptr + row + 1) - beg;
   const int n_stages = (deg + kHvEdges - 1) / kHvEdges;
   const int* ind = indices + beg;
   const float* val = vals + beg;
-  const float* xbase = X + (size_t)slab32 * 32;
+  const float* xbase = X + (size_t)sub * kSlab;
 
   auto issue_idx = [&](int s) {
     if (s < n_stages) {
       const int e = s * kHvEdges + lane;
       if (e < deg) {
-        cp_async4(&idx_s[s % kHvISlots][lane], ind + e);
-        cp_async4(&val_s[s % kHvISlots][lane], val + e);
+        cp_async4(&idx_s[s & (kHvISlots - 1)][lane], ind + e);
+        cp_async4(&val_s[s & (kHvISlots - 1)][lane], val + e);
       }
     }
   };
   auto issue_gather = [&](int s) {
     if (s < n_stages) {
+      constexpr int kCopies = kHvEdges / kRowsPerCopy;
       const int cnt = min(kHvEdges, deg - s * kHvEdges);
-      const int part = (lane & 7) * 4;
+      const int part = (lane % kLanesPerRow) * 4;
+      const int* it = idx_s[s & (kHvISlots - 1)];
+      float(*xt)[kSlab] = xs[s & (kHvXSlots - 1)];
+      // All column indices are read before the first copy is issued: the copies
+      // are ordered against shared-memory reads, so a read placed between two of
+      // them would serialise the whole sequence on its latency.
+      int c[kCopies];
 #pragma unroll
-      for (int k = 0; k < kHvEdges / 4; ++k) {
-        const int e = (lane >> 3) + 4 * k;
-        if (e < cnt) {
-          const int c = idx_s[s % kHvISlots][e];
-          cp_async16_cg(&xs[s % kHvXSlots][e][part], xbase + (size_t)c * F + part);
-        }
+      for (int k = 0; k < kCopies; ++k) c[k] = it[lane / kLanesPerRow + kRowsPerCopy * k];
+#pragma unroll
+      for (int k = 0; k < kCopies; ++k) {
+        const int e = lane / kLanesPerRow + kRowsPerCopy * k;
+        if (e < cnt) cp_async16_cg(&xt[e][part], xbase + (size_t)c[k] * F + part);
       }
     }
   };
@@ -155,7 +197,8 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     cp_async_commit();
   }
 
-  float acc = 0.f;
+  float acc1 = 0.f;
+  float2 acc2 = make_float2(0.f, 0.f);
   for (int i = 0; i < n_stages; ++i) {
     cp_async_wait<kHvDist - 1>();  // stage i's gathers and stage i+D's indices landed
     __syncwarp();                  // ... for every lane; stage i-1 is fully consumed
@@ -163,24 +206,38 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     issue_idx(i + 2 * kHvDist);
     cp_async_commit();
 
-    const float(*xt)[32] = xs[i % kHvXSlots];
-    const float* vt = val_s[i % kHvISlots];
+    const float(*xt)[kSlab] = xs[i & (kHvXSlots - 1)];
+    const float* vt = val_s[i & (kHvISlots - 1)];
     const int cnt = min(kHvEdges, deg - i * kHvEdges);
     if (cnt == kHvEdges) {
 #pragma unroll
       for (int e4 = 0; e4 < kHvEdges; e4 += 4) {
         const float4 v4 = *reinterpret_cast<const float4*>(vt + e4);
-        acc = mul_then_add(acc, v4.x, xt[e4 + 0][lane]);
-        acc = mul_then_add(acc, v4.y, xt[e4 + 1][lane]);
-        acc = mul_then_add(acc, v4.z, xt[e4 + 2][lane]);
-        acc = mul_then_add(acc, v4.w, xt[e4 + 3][lane]);
+        const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (VEC == 2)
+            acc2 = mul_then_add2(acc2, vv[q],
+                                 *reinterpret_cast<const float2*>(&xt[e4 + q][lane * VEC]));
+          else
+            acc1 = mul_then_add(acc1, vv[q], xt[e4 + q][lane * VEC]);
+        }
       }
     } else {
-      for (int e = 0; e < cnt; ++e) acc = mul_then_add(acc, vt[e], xt[e][lane]);
+      for (int e = 0; e < cnt; ++e) {
+        if (VEC == 2)
+          acc2 = mul_then_add2(acc2, vt[e], *reinterpret_cast<const float2*>(&xt[e][lane * VEC]));
+        else
+          acc1 = mul_then_add(acc1, vt[e], xt[e][lane * VEC]);
+      }
     }
   }
   cp_async_wait<0>();
-  __stcs(Y + (size_t)row * F + (size_t)slab32 * 32 + lane, acc);
+  float* yout = Y + (size_t)row * F + (size_t)sub * kSlab + lane * VEC;
+  if (VEC == 2)
+    __stcs(reinterpret_cast<float2*>(yout), acc2);
+  else
+    __stcs(yout, acc1);
 }
 
 // Fallback for any feat_len / alignment: one warp per row, lanes over features.
@@ -213,6 +270,7 @@ struct fg_spmm_plan {
   int feat_len = 0;
   bool vector_ok = false;  // feat_len % 32 == 0
   int slab_w = 0;          // floats per light item (32, 64 or 128)
+  int heavy_vec = 1;       // floats per lane of the heavy kernel (1 or 2)
   int heavy_threshold = 0;
   int n_light = 0, n_heavy = 0;
   int64_t max_deg = 0, heavy_nnz = 0;
@@ -301,6 +359,7 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
 
   FG_PLAN_TRY(cudaDeviceGetAttribute(&p->l2_bytes, cudaDevAttrL2CacheSize, device));
   p->slab_w = choose_slab_width(feat_len, n_cols, p->l2_bytes);
+  p->heavy_vec = (p->slab_w % 64 == 0) ? 2 : 1;
 
   if (p->vector_ok && n_rows > 0) {
     // Stable counting sort of the rows by degree, descending: the hardware
@@ -332,6 +391,12 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
       FG_PLAN_TRY(cudaMalloc(&p->heavy_rows_dev, sizeof(int32_t) * (size_t)p->n_heavy));
       FG_PLAN_TRY(cudaMemcpy(p->heavy_rows_dev, order.data(), sizeof(int32_t) * (size_t)p->n_heavy,
                              cudaMemcpyHostToDevice));
+      FG_PLAN_TRY(cudaFuncSetAttribute(spmm_heavy_kernel<1>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       heavy_smem_bytes<1>()));
+      FG_PLAN_TRY(cudaFuncSetAttribute(spmm_heavy_kernel<2>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       heavy_smem_bytes<2>()));
       int lo = 0, hi = 0;
       FG_PLAN_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
       FG_PLAN_TRY(cudaStreamCreateWithPriority(&p->aux, cudaStreamNonBlocking, hi));
@@ -366,16 +431,16 @@ extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t b
   if (p->vector_ok) {
     const int G = p->slab_w / 4;
     const long long light_items = (long long)p->n_light * (p->feat_len / p->slab_w);
-    const long long heavy_items = (long long)p->n_heavy * (p->feat_len / 32);
+    const long long heavy_items = (long long)p->n_heavy * (p->feat_len / (32 * p->heavy_vec));
     snprintf(buf, (size_t)buf_len,
              "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d | L2=%d B slab_w=%d | "
              "light: %d rows (deg<=%d) -> spmm_light_kernel<G=%d> grid=%lld x 256 thr | "
-             "heavy: %d rows, %lld nnz, max_deg=%lld -> spmm_heavy_kernel grid=%lld x 32 thr, "
+             "heavy: %d rows, %lld nnz, max_deg=%lld -> spmm_heavy_kernel<VEC=%d> grid=%lld x 32 thr, "
              "%d-stage cp.async ring, aux stream",
              (long long)p->n_rows, (long long)p->n_cols, (long long)p->nnz, p->feat_len,
              p->l2_bytes, p->slab_w, p->n_light, p->heavy_threshold, G,
              (light_items + 256 / G - 1) / (256 / G), p->n_heavy, (long long)p->heavy_nnz,
-             (long long)p->max_deg, heavy_items, kHvDist);
+             (long long)p->max_deg, p->heavy_vec, heavy_items, kHvDist);
   } else {
     snprintf(buf, (size_t)buf_len,
              "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d | spmm_generic_kernel "
@@ -432,11 +497,17 @@ extern "C" int fg_spmm_csr_f32(const fg_spmm_plan* p, const int32_t* indptr,
     // light kernel fills the rest of the machine; join before returning.
     FG_CUDA_TRY(cudaEventRecord(p->fork_ev, st));
     FG_CUDA_TRY(cudaStreamWaitEvent(p->aux, p->fork_ev, 0));
-    const long long items = (long long)p->n_heavy * (p->feat_len / 32);
+    const int slab = 32 * p->heavy_vec;
+    const long long items = (long long)p->n_heavy * (p->feat_len / slab);
     if (items >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "too many heavy items");
-    spmm_heavy_kernel<<<(unsigned)items, 32, 0, p->aux>>>(indptr, indices, vals, x, y,
-                                                          p->heavy_rows_dev, p->n_heavy,
-                                                          p->slab_w / 32, p->feat_len);
+    if (p->heavy_vec == 2)
+      spmm_heavy_kernel<2><<<(unsigned)items, 32, heavy_smem_bytes<2>(), p->aux>>>(
+          indptr, indices, vals, x, y, p->heavy_rows_dev, p->n_heavy, p->slab_w / slab,
+          p->feat_len);
+    else
+      spmm_heavy_kernel<1><<<(unsigned)items, 32, heavy_smem_bytes<1>(), p->aux>>>(
+          indptr, indices, vals, x, y, p->heavy_rows_dev, p->n_heavy, p->slab_w / slab,
+          p->feat_len);
     FG_CUDA_TRY(cudaGetLastError());
     FG_CUDA_TRY(cudaEventRecord(p->join_ev, p->aux));
   }

@@ -26,7 +26,7 @@ class FeatGraphError(RuntimeError):
 EXPORTED_SYMBOLS = (
     "fg_last_error_string", "fg_version",
     "fg_spmm_plan_create", "fg_spmm_plan_destroy", "fg_spmm_plan_describe",
-    "fg_spmm_plan_num_launches", "fg_spmm_csr_f32", "fg_spmm_csr_f32_host",
+    "fg_spmm_plan_num_launches", "fg_spmm_plan_status", "fg_spmm_csr_f32", "fg_spmm_csr_f32_host",
     "fg_spmm_csr_f32_noalloc", "fg_spmm_noalloc_max_rows",
     "fg_sddmm_coo_f32", "fg_sddmm_coo_f32_host", "fg_sddmm_num_launches", "fg_sddmm_describe",
     "fg_shard_rows_by_nnz", "fg_shard_edges",
@@ -50,6 +50,7 @@ def load():
     lib.fg_spmm_plan_destroy.argtypes = [c_void]
     lib.fg_spmm_plan_describe.argtypes = [c_void, ctypes.c_char_p, i64]
     lib.fg_spmm_plan_num_launches.argtypes = [c_void]
+    lib.fg_spmm_plan_status.argtypes = [c_void, c_i32p]
     lib.fg_spmm_csr_f32.argtypes = [c_void] * 7
     lib.fg_spmm_csr_f32_host.argtypes = [c_void] * 9
     lib.fg_spmm_csr_f32_noalloc.argtypes = [c_void] * 5 + [i64, i64, i32, i32, c_void]

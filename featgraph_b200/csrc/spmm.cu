@@ -112,13 +112,69 @@ spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
 }
 
 constexpr int kHvEdges = 32;    // nonzeros per stage
-constexpr int kHvXSlots = 8;    // ring of gathered X segments (power of two)
+constexpr int kHvXSlots = 4;    // ring of gathered X segments (power of two)
 constexpr int kHvDist = kHvXSlots - 1;  // stages of gathers in flight
-constexpr int kHvISlots = 16;   // ring of index/value tiles, >= 2 * kHvDist + 1
+constexpr int kHvISlots = 8;    // ring of index/value tiles, >= 2 * kHvDist + 1
 
 template <int VEC>
 constexpr int heavy_smem_bytes() {
   return kHvXSlots * kHvEdges * 32 * VEC * 4 + kHvISlots * kHvEdges * 8;
+}
+
+// Adds one stage (cnt <= 32 gathered segments, in CSR order) to a lane's
+// accumulators; xt[e] is the segment of nonzero e, vt[e] its value.
+template <int VEC>
+__device__ __forceinline__ void heavy_consume_stage(const float (*xt)[32 * VEC], const float* vt,
+                                                    int cnt, int lane, float& acc_a,
+                                                    float& acc_b) {
+  if (cnt == kHvEdges) {
+#pragma unroll
+    for (int e4 = 0; e4 < kHvEdges; e4 += 4) {
+      const float4 v4 = *reinterpret_cast<const float4*>(vt + e4);
+      const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (VEC == 2) {
+          const float2 xv = *reinterpret_cast<const float2*>(&xt[e4 + q][lane * 2]);
+          acc_a = mul_then_add(acc_a, vv[q], xv.x);
+          acc_b = mul_then_add(acc_b, vv[q], xv.y);
+        } else {
+          acc_a = mul_then_add(acc_a, vv[q], xt[e4 + q][lane]);
+        }
+      }
+    }
+  } else {
+    for (int e = 0; e < cnt; ++e) {
+      if (VEC == 2) {
+        const float2 xv = *reinterpret_cast<const float2*>(&xt[e][lane * 2]);
+        acc_a = mul_then_add(acc_a, vt[e], xv.x);
+        acc_b = mul_then_add(acc_b, vt[e], xv.y);
+      } else {
+        acc_a = mul_then_add(acc_a, vt[e], xt[e][lane]);
+      }
+    }
+  }
+}
+
+template <int VEC>
+__device__ __forceinline__ void heavy_store_row(float* yslab, int lane, float acc_a, float acc_b) {
+  if (VEC == 2)
+    __stcs(reinterpret_cast<float2*>(yslab + lane * 2), make_float2(acc_a, acc_b));
+  else
+    __stcs(yslab + lane, acc_a);
+}
+
+// Decodes blockIdx.x of the heavy / giant kernels: items are ordered
+// (residency slab, row, sub-slab) so that the sub-slabs of one row run side by
+// side and share their index stream in L2.
+__device__ __forceinline__ void heavy_decode_item(const int* __restrict__ rows, int n_listed,
+                                                  int subs_per_slab, int& row, int& sub) {
+  const long long item = blockIdx.x;
+  const long long per_slab = (long long)n_listed * subs_per_slab;
+  const int ss = (int)(item / per_slab);
+  const long long rem = item - ss * per_slab;
+  row = __ldg(rows + rem / subs_per_slab);
+  sub = ss * subs_per_slab + (int)(rem % subs_per_slab);
 }
 
 // One warp per (heavy row, 32*VEC-float slab); VEC = floats per lane (1 or 2).
@@ -139,14 +195,8 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
       heavy_smem + kHvXSlots * kHvEdges * kSlab * 4 + kHvISlots * kHvEdges * 4);
 
   const int lane = threadIdx.x;
-  // Item order: (residency slab, row, sub-slab) so that the sub-slabs of one
-  // row run side by side and share their index stream in L2.
-  const long long item = blockIdx.x;
-  const long long per_slab = (long long)n_listed * subs_per_slab;
-  const int ss = (int)(item / per_slab);
-  const long long rem = item - ss * per_slab;
-  const int row = __ldg(rows + rem / subs_per_slab);
-  const int sub = ss * subs_per_slab + (int)(rem % subs_per_slab);
+  int row, sub;
+  heavy_decode_item(rows, n_listed, subs_per_slab, row, sub);
 
   const int beg = __ldg(indptr + row);
   const int deg = __ldg(indptr + row + 1) - beg;
@@ -197,47 +247,146 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     cp_async_commit();
   }
 
-  float acc1 = 0.f;
-  float2 acc2 = make_float2(0.f, 0.f);
+  // Two scalar chains per lane (VEC == 2) rather than one packed add: on this
+  // latency-bound path the packed fp32x2 add is the slower dependency.
+  float acc_a = 0.f, acc_b = 0.f;
   for (int i = 0; i < n_stages; ++i) {
     cp_async_wait<kHvDist - 1>();  // stage i's gathers and stage i+D's indices landed
     __syncwarp();                  // ... for every lane; stage i-1 is fully consumed
     issue_gather(i + kHvDist);
     issue_idx(i + 2 * kHvDist);
     cp_async_commit();
-
-    const float(*xt)[kSlab] = xs[i & (kHvXSlots - 1)];
-    const float* vt = val_s[i & (kHvISlots - 1)];
-    const int cnt = min(kHvEdges, deg - i * kHvEdges);
-    if (cnt == kHvEdges) {
-#pragma unroll
-      for (int e4 = 0; e4 < kHvEdges; e4 += 4) {
-        const float4 v4 = *reinterpret_cast<const float4*>(vt + e4);
-        const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (VEC == 2)
-            acc2 = mul_then_add2(acc2, vv[q],
-                                 *reinterpret_cast<const float2*>(&xt[e4 + q][lane * VEC]));
-          else
-            acc1 = mul_then_add(acc1, vv[q], xt[e4 + q][lane * VEC]);
-        }
-      }
-    } else {
-      for (int e = 0; e < cnt; ++e) {
-        if (VEC == 2)
-          acc2 = mul_then_add2(acc2, vt[e], *reinterpret_cast<const float2*>(&xt[e][lane * VEC]));
-        else
-          acc1 = mul_then_add(acc1, vt[e], xt[e][lane * VEC]);
-      }
-    }
+    heavy_consume_stage<VEC>(xs[i & (kHvXSlots - 1)], val_s[i & (kHvISlots - 1)],
+                             min(kHvEdges, deg - i * kHvEdges), lane, acc_a, acc_b);
   }
   cp_async_wait<0>();
-  float* yout = Y + (size_t)row * F + (size_t)sub * kSlab + lane * VEC;
-  if (VEC == 2)
-    __stcs(reinterpret_cast<float2*>(yout), acc2);
-  else
-    __stcs(yout, acc1);
+  heavy_store_row<VEC>(Y + (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
+}
+
+constexpr int kGtProducers = 7;   // producer warps per CTA
+constexpr int kGtSlots = 16;      // ring of stages (power of two)
+constexpr int kGtQueue = 4;       // stages of column indices a producer holds in registers
+constexpr unsigned kGtMaxPolls = 1u << 24;  // bound of every barrier wait
+constexpr int kGtErrProducerTimeout = 1, kGtErrConsumerTimeout = 2;
+
+template <int VEC>
+constexpr int giant_smem_bytes() {
+  return kGtSlots * kHvEdges * 32 * VEC * 4   // gathered X segments
+         + kGtSlots * kHvEdges * 4            // values
+         + 2 * kGtSlots * 8;                  // full / empty barriers
+}
+
+// One CTA of 1 consumer + kGtProducers producer warps per (giant row, slab).
+//
+// The sum of one row is a dependent chain (CSR order, one accumulator per
+// feature), so the longest row bounds the whole SpMM.  A single warp cannot feed
+// that chain: it can keep only a few cp.async copies outstanding (measured: 85
+// cycles per 512-byte copy instruction for a lone warp, i.e. 47 cycles per
+// nonzero at 64 features, while the chain itself needs 4 to 6).  Here producer
+// warp w gathers stages w, w+P, w+2P, ... (column indices through a register
+// queue, 16-byte cp.async copies that signal the stage's "full" mbarrier when
+// they land) and the consumer warp adds the stages in order and hands slots
+// back through "empty" mbarriers.  Every barrier wait is a bounded poll; a wait
+// that gives up records a code in *status and the warp leaves.
+template <int VEC>
+__global__ void __launch_bounds__(32 * (kGtProducers + 1))
+spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
+                  const float* __restrict__ vals, const float* __restrict__ X,
+                  float* __restrict__ Y, const int* __restrict__ rows, int n_listed,
+                  int subs_per_slab, int F, int* __restrict__ status) {
+  constexpr unsigned kFull = 0xffffffffu;
+  constexpr int kSlab = 32 * VEC;
+  constexpr int kLanesPerRow = kSlab / 4;
+  constexpr int kRowsPerCopy = 32 / kLanesPerRow;
+  constexpr int kCopies = kHvEdges / kRowsPerCopy;
+  extern __shared__ __align__(16) unsigned char giant_smem[];
+  float(*xs)[kHvEdges][kSlab] = reinterpret_cast<float(*)[kHvEdges][kSlab]>(giant_smem);
+  float(*val_s)[kHvEdges] =
+      reinterpret_cast<float(*)[kHvEdges]>(giant_smem + kGtSlots * kHvEdges * kSlab * 4);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(giant_smem + kGtSlots * kHvEdges * kSlab * 4 +
+                                                   kGtSlots * kHvEdges * 4);
+  uint64_t* empty_bar = full_bar + kGtSlots;
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  int row, sub;
+  heavy_decode_item(rows, n_listed, subs_per_slab, row, sub);
+  const int beg = __ldg(indptr + row);
+  const int deg = __ldg(indptr + row + 1) - beg;
+  const int n_stages = (deg + kHvEdges - 1) / kHvEdges;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kGtSlots; ++i) {
+      mbar_init(&full_bar[i], 32);  // one arrival per lane of the producing warp
+      mbar_init(&empty_bar[i], 1);  // one arrival by the consumer
+    }
+  }
+  __syncthreads();
+
+  if (warp > 0) {
+    // ------------------------------------------------------------ producer --
+    const int* ind = indices + beg;
+    const float* val = vals + beg;
+    const int part = (lane % kLanesPerRow) * 4;
+    const int first = lane / kLanesPerRow;
+    const float* xbase = X + (size_t)sub * kSlab + part;
+    const int s_first = warp - 1;
+    int idxq[kGtQueue];
+#pragma unroll
+    for (int u = 0; u < kGtQueue; ++u) {
+      const long long e = (long long)(s_first + u * kGtProducers) * kHvEdges + lane;
+      idxq[u] = e < deg ? ld_stream(ind + e) : 0;
+    }
+    bool ok = true;
+    for (int s0 = s_first; s0 < n_stages && ok; s0 += kGtQueue * kGtProducers) {
+#pragma unroll
+      for (int u = 0; u < kGtQueue; ++u) {
+        const int s = s0 + u * kGtProducers;
+        if (s < n_stages && ok) {
+          const int slot = s & (kGtSlots - 1);
+          const unsigned round = (unsigned)(s / kGtSlots);
+          // slot handed back by the consumer?  (passes at once in round 0)
+          ok = mbar_wait_bounded(&empty_bar[slot], (round & 1u) ^ 1u, kGtMaxPolls);
+          if (ok) {
+            const int cnt = min(kHvEdges, deg - s * kHvEdges);
+            const int my_idx = idxq[u];
+            const long long e_ahead =
+                (long long)(s + kGtQueue * kGtProducers) * kHvEdges + lane;
+            idxq[u] = e_ahead < deg ? ld_stream(ind + e_ahead) : 0;
+            if (lane < cnt) cp_async4(&val_s[slot][lane], val + s * kHvEdges + lane);
+#pragma unroll
+            for (int k = 0; k < kCopies; ++k) {
+              const int e = first + kRowsPerCopy * k;
+              const int c = __shfl_sync(kFull, my_idx, e);
+              if (e < cnt) cp_async16_cg(&xs[slot][e][part], xbase + (size_t)c * F);
+            }
+            cp_async_arrive_on(&full_bar[slot]);
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicExch(status, kGtErrProducerTimeout);
+    cp_async_wait_all();
+    return;
+  }
+
+  // -------------------------------------------------------------- consumer --
+  float acc_a = 0.f, acc_b = 0.f;
+  bool ok = true;
+  for (int i = 0; i < n_stages; ++i) {
+    const int slot = i & (kGtSlots - 1);
+    ok = mbar_wait_bounded(&full_bar[slot], (unsigned)(i / kGtSlots) & 1u, kGtMaxPolls);
+    if (!ok) break;
+    heavy_consume_stage<VEC>(xs[slot], val_s[slot], min(kHvEdges, deg - i * kHvEdges), lane,
+                             acc_a, acc_b);
+    __syncwarp();  // every lane has read the slot
+    if (lane == 0) mbar_arrive(&empty_bar[slot]);
+  }
+  if (!ok) {
+    if (lane == 0) atomicExch(status, kGtErrConsumerTimeout);
+    return;  // the row is not written; the host sees the status
+  }
+  heavy_store_row<VEC>(Y + (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
 }
 
 // Fallback for any feat_len / alignment: one warp per row, lanes over features.
@@ -270,29 +419,33 @@ struct fg_spmm_plan {
   int feat_len = 0;
   bool vector_ok = false;  // feat_len % 32 == 0
   int slab_w = 0;          // floats per light item (32, 64 or 128)
-  int heavy_vec = 1;       // floats per lane of the heavy kernel (1 or 2)
-  int heavy_threshold = 0;
-  int n_light = 0, n_heavy = 0;
-  int64_t max_deg = 0, heavy_nnz = 0;
-  int* light_rows_dev = nullptr;
-  int* heavy_rows_dev = nullptr;
-  cudaStream_t aux = nullptr;
-  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
-  int l2_bytes = 0;
+  int heavy_vec = 1;       // floats per lane of the heavy / giant kernels (1 or 2)
+  int heavy_threshold = 0, giant_threshold = 0;
+  // rows sorted by degree, descending: [0, n_giant) giant, then n_heavy heavy, then light
+  int n_giant = 0, n_heavy = 0, n_light = 0;
+  int64_t max_deg = 0, giant_nnz = 0, heavy_nnz = 0;
+  int* rows_dev = nullptr;    // the whole sorted list
+  int* status_dev = nullptr;  // set by a giant-kernel barrier wait that gave up
+  cudaStream_t aux_giant = nullptr, aux_heavy = nullptr;
+  cudaEvent_t fork_ev = nullptr, join_giant = nullptr, join_heavy = nullptr;
+  int l2_bytes = 0, n_sms = 0;
 };
 
 namespace fg {
 
 constexpr int kDefaultHeavyThreshold = 2048;
+constexpr int kDefaultGiantThreshold = 32768;
 
 static void plan_release(fg_spmm_plan* p) {
   if (!p) return;
   DeviceGuard g(p->device);
-  if (p->light_rows_dev) cudaFree(p->light_rows_dev);
-  if (p->heavy_rows_dev) cudaFree(p->heavy_rows_dev);
+  if (p->rows_dev) cudaFree(p->rows_dev);
+  if (p->status_dev) cudaFree(p->status_dev);
   if (p->fork_ev) cudaEventDestroy(p->fork_ev);
-  if (p->join_ev) cudaEventDestroy(p->join_ev);
-  if (p->aux) cudaStreamDestroy(p->aux);
+  if (p->join_giant) cudaEventDestroy(p->join_giant);
+  if (p->join_heavy) cudaEventDestroy(p->join_heavy);
+  if (p->aux_giant) cudaStreamDestroy(p->aux_giant);
+  if (p->aux_heavy) cudaStreamDestroy(p->aux_heavy);
   delete p;
 }
 
@@ -339,6 +492,10 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
   p->feat_len = feat_len;
   p->max_deg = max_deg;
   p->heavy_threshold = heavy_threshold > 0 ? heavy_threshold : kDefaultHeavyThreshold;
+  // An explicit threshold (tests use tiny ones) also scales the giant class down.
+  p->giant_threshold =
+      heavy_threshold > 0 ? std::min(kDefaultGiantThreshold, 16 * heavy_threshold)
+                          : kDefaultGiantThreshold;
   p->vector_ok = (feat_len % 32 == 0);
 
   DeviceGuard guard(device);
@@ -358,6 +515,7 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
   } while (0)
 
   FG_PLAN_TRY(cudaDeviceGetAttribute(&p->l2_bytes, cudaDevAttrL2CacheSize, device));
+  FG_PLAN_TRY(cudaDeviceGetAttribute(&p->n_sms, cudaDevAttrMultiProcessorCount, device));
   p->slab_w = choose_slab_width(feat_len, n_cols, p->l2_bytes);
   p->heavy_vec = (p->slab_w % 64 == 0) ? 2 : 1;
 
@@ -377,36 +535,48 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
     std::vector<int32_t> order((size_t)n_rows);
     for (int64_t r = 0; r < n_rows; ++r)
       order[(size_t)start[(size_t)(indptr[r + 1] - indptr[r])]++] = (int32_t)r;
-    int64_t n_heavy = 0, heavy_nnz = 0;
-    while (n_heavy < n_rows) {
-      const int64_t d = indptr[order[(size_t)n_heavy] + 1] - indptr[order[(size_t)n_heavy]];
-      if (d <= p->heavy_threshold) break;
-      heavy_nnz += d;
-      ++n_heavy;
-    }
-    p->n_heavy = (int)n_heavy;
-    p->n_light = (int)(n_rows - n_heavy);
-    p->heavy_nnz = heavy_nnz;
-    if (p->n_heavy > 0) {
-      FG_PLAN_TRY(cudaMalloc(&p->heavy_rows_dev, sizeof(int32_t) * (size_t)p->n_heavy));
-      FG_PLAN_TRY(cudaMemcpy(p->heavy_rows_dev, order.data(), sizeof(int32_t) * (size_t)p->n_heavy,
-                             cudaMemcpyHostToDevice));
-      FG_PLAN_TRY(cudaFuncSetAttribute(spmm_heavy_kernel<1>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       heavy_smem_bytes<1>()));
-      FG_PLAN_TRY(cudaFuncSetAttribute(spmm_heavy_kernel<2>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       heavy_smem_bytes<2>()));
+    auto degree_at = [&](int64_t k) {
+      return (int64_t)indptr[order[(size_t)k] + 1] - indptr[order[(size_t)k]];
+    };
+    // Giant class: rows over the giant threshold, but no more (row, slab) CTAs
+    // than SMs -- a giant CTA wants an SM's worth of copy bandwidth to itself.
+    const int64_t giant_cap = std::max<int64_t>(1, p->n_sms / (feat_len / (32 * p->heavy_vec)));
+    int64_t k = 0;
+    while (k < n_rows && k < giant_cap && degree_at(k) > p->giant_threshold) p->giant_nnz += degree_at(k++);
+    p->n_giant = (int)k;
+    while (k < n_rows && degree_at(k) > p->heavy_threshold) p->heavy_nnz += degree_at(k++);
+    p->n_heavy = (int)(k - p->n_giant);
+    p->n_light = (int)(n_rows - k);
+
+    FG_PLAN_TRY(cudaMalloc(&p->rows_dev, sizeof(int32_t) * (size_t)n_rows));
+    FG_PLAN_TRY(cudaMemcpy(p->rows_dev, order.data(), sizeof(int32_t) * (size_t)n_rows,
+                           cudaMemcpyHostToDevice));
+    if (p->n_giant + p->n_heavy > 0) {
       int lo = 0, hi = 0;
       FG_PLAN_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-      FG_PLAN_TRY(cudaStreamCreateWithPriority(&p->aux, cudaStreamNonBlocking, hi));
       FG_PLAN_TRY(cudaEventCreateWithFlags(&p->fork_ev, cudaEventDisableTiming));
-      FG_PLAN_TRY(cudaEventCreateWithFlags(&p->join_ev, cudaEventDisableTiming));
-    }
-    if (p->n_light > 0) {
-      FG_PLAN_TRY(cudaMalloc(&p->light_rows_dev, sizeof(int32_t) * (size_t)p->n_light));
-      FG_PLAN_TRY(cudaMemcpy(p->light_rows_dev, order.data() + n_heavy,
-                             sizeof(int32_t) * (size_t)p->n_light, cudaMemcpyHostToDevice));
+      if (p->n_giant > 0) {
+        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_giant_kernel<1>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         giant_smem_bytes<1>()));
+        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_giant_kernel<2>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         giant_smem_bytes<2>()));
+        FG_PLAN_TRY(cudaStreamCreateWithPriority(&p->aux_giant, cudaStreamNonBlocking, hi));
+        FG_PLAN_TRY(cudaEventCreateWithFlags(&p->join_giant, cudaEventDisableTiming));
+        FG_PLAN_TRY(cudaMalloc(&p->status_dev, sizeof(int)));
+        FG_PLAN_TRY(cudaMemset(p->status_dev, 0, sizeof(int)));
+      }
+      if (p->n_heavy > 0) {
+        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_heavy_kernel<1>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         heavy_smem_bytes<1>()));
+        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_heavy_kernel<2>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         heavy_smem_bytes<2>()));
+        FG_PLAN_TRY(cudaStreamCreateWithPriority(&p->aux_heavy, cudaStreamNonBlocking, hi));
+        FG_PLAN_TRY(cudaEventCreateWithFlags(&p->join_heavy, cudaEventDisableTiming));
+      }
     }
   }
 #undef FG_PLAN_TRY
@@ -419,10 +589,26 @@ extern "C" int fg_spmm_plan_destroy(fg_spmm_plan* plan) {
   return FG_OK;
 }
 
+extern "C" int fg_spmm_plan_status(const fg_spmm_plan* p, int32_t* device_status) {
+  using namespace fg;
+  if (!p || !device_status) return fail(FG_ERR_INVALID_ARGUMENT, "null plan or output");
+  *device_status = 0;
+  if (!p->status_dev) return FG_OK;
+  DeviceGuard guard(p->device);
+  FG_CUDA_TRY(cudaDeviceSynchronize());
+  int v = 0;
+  FG_CUDA_TRY(cudaMemcpy(&v, p->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+  *device_status = v;
+  if (v != 0)
+    return fail(FG_ERR_CUDA, "spmm_giant_kernel: a bounded barrier wait gave up (code %d: %s warp)",
+                v, v == kGtErrProducerTimeout ? "producer" : "consumer");
+  return FG_OK;
+}
+
 extern "C" int fg_spmm_plan_num_launches(const fg_spmm_plan* p) {
   if (!p || p->n_rows == 0) return 0;
   if (!p->vector_ok) return 1;
-  return (p->n_heavy > 0 ? 1 : 0) + (p->n_light > 0 ? 1 : 0);
+  return (p->n_giant > 0 ? 1 : 0) + (p->n_heavy > 0 ? 1 : 0) + (p->n_light > 0 ? 1 : 0);
 }
 
 extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t buf_len) {
@@ -430,17 +616,21 @@ extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t b
   if (!p || !buf || buf_len <= 0) return fail(FG_ERR_INVALID_ARGUMENT, "null plan or buffer");
   if (p->vector_ok) {
     const int G = p->slab_w / 4;
+    const int hv_slabs = p->feat_len / (32 * p->heavy_vec);
     const long long light_items = (long long)p->n_light * (p->feat_len / p->slab_w);
-    const long long heavy_items = (long long)p->n_heavy * (p->feat_len / (32 * p->heavy_vec));
     snprintf(buf, (size_t)buf_len,
-             "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d | L2=%d B slab_w=%d | "
-             "light: %d rows (deg<=%d) -> spmm_light_kernel<G=%d> grid=%lld x 256 thr | "
-             "heavy: %d rows, %lld nnz, max_deg=%lld -> spmm_heavy_kernel<VEC=%d> grid=%lld x 32 thr, "
-             "%d-stage cp.async ring, aux stream",
+             "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d max_deg=%lld | L2=%d B "
+             "slab_w=%d | light: %d rows (deg<=%d) -> spmm_light_kernel<G=%d> grid=%lld x 256 thr | "
+             "heavy: %d rows (deg<=%d), %lld nnz -> spmm_heavy_kernel<VEC=%d> grid=%lld x 32 thr, "
+             "%d-stage cp.async ring, own stream | giant: %d rows, %lld nnz -> "
+             "spmm_giant_kernel<VEC=%d> grid=%lld x %d thr (%d producer warps + 1 consumer, "
+             "%d-slot ring, mbarriers), own stream",
              (long long)p->n_rows, (long long)p->n_cols, (long long)p->nnz, p->feat_len,
-             p->l2_bytes, p->slab_w, p->n_light, p->heavy_threshold, G,
-             (light_items + 256 / G - 1) / (256 / G), p->n_heavy, (long long)p->heavy_nnz,
-             (long long)p->max_deg, p->heavy_vec, heavy_items, kHvDist);
+             (long long)p->max_deg, p->l2_bytes, p->slab_w, p->n_light, p->heavy_threshold, G,
+             (light_items + 256 / G - 1) / (256 / G), p->n_heavy, p->giant_threshold,
+             (long long)p->heavy_nnz, p->heavy_vec, (long long)p->n_heavy * hv_slabs, kHvXSlots,
+             p->n_giant, (long long)p->giant_nnz, p->heavy_vec, (long long)p->n_giant * hv_slabs,
+             32 * (kGtProducers + 1), kGtProducers, kGtSlots);
   } else {
     snprintf(buf, (size_t)buf_len,
              "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d | spmm_generic_kernel "
@@ -460,9 +650,9 @@ static void launch_light(const fg_spmm_plan* p, const int32_t* indptr, const int
                          const float* vals, const float* x, float* y, cudaStream_t st) {
   const long long items = (long long)p->n_light * (p->feat_len / (4 * G));
   const long long grid = (items + 256 / G - 1) / (256 / G);
-  spmm_light_kernel<G><<<(unsigned)grid, 256, 0, st>>>(indptr, indices, vals, x, y,
-                                                        p->light_rows_dev, p->n_light, items,
-                                                        p->feat_len);
+  spmm_light_kernel<G><<<(unsigned)grid, 256, 0, st>>>(
+      indptr, indices, vals, x, y, p->rows_dev + p->n_giant + p->n_heavy, p->n_light, items,
+      p->feat_len);
 }
 
 }  // namespace fg
@@ -492,24 +682,41 @@ extern "C" int fg_spmm_csr_f32(const fg_spmm_plan* p, const int32_t* indptr,
     return FG_OK;
   }
 
+  // Fork: giant and heavy rows run on the plan's own high-priority streams, the
+  // longest first, while the light kernel fills the rest of the machine; the
+  // caller's stream joins both before the call returns control to it.
+  const int slab = 32 * p->heavy_vec;
+  const int hv_slabs = p->feat_len / slab;
+  if (p->fork_ev) FG_CUDA_TRY(cudaEventRecord(p->fork_ev, st));
+  if (p->n_giant > 0) {
+    FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_giant, p->fork_ev, 0));
+    const unsigned grid = (unsigned)(p->n_giant * hv_slabs);
+    const unsigned threads = 32 * (kGtProducers + 1);
+    if (p->heavy_vec == 2)
+      spmm_giant_kernel<2><<<grid, threads, giant_smem_bytes<2>(), p->aux_giant>>>(
+          indptr, indices, vals, x, y, p->rows_dev, p->n_giant, p->slab_w / slab, p->feat_len,
+          p->status_dev);
+    else
+      spmm_giant_kernel<1><<<grid, threads, giant_smem_bytes<1>(), p->aux_giant>>>(
+          indptr, indices, vals, x, y, p->rows_dev, p->n_giant, p->slab_w / slab, p->feat_len,
+          p->status_dev);
+    FG_CUDA_TRY(cudaGetLastError());
+    FG_CUDA_TRY(cudaEventRecord(p->join_giant, p->aux_giant));
+  }
   if (p->n_heavy > 0) {
-    // Fork: the heavy rows run on the plan's high-priority stream while the
-    // light kernel fills the rest of the machine; join before returning.
-    FG_CUDA_TRY(cudaEventRecord(p->fork_ev, st));
-    FG_CUDA_TRY(cudaStreamWaitEvent(p->aux, p->fork_ev, 0));
-    const int slab = 32 * p->heavy_vec;
-    const long long items = (long long)p->n_heavy * (p->feat_len / slab);
+    FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_heavy, p->fork_ev, 0));
+    const long long items = (long long)p->n_heavy * hv_slabs;
     if (items >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "too many heavy items");
     if (p->heavy_vec == 2)
-      spmm_heavy_kernel<2><<<(unsigned)items, 32, heavy_smem_bytes<2>(), p->aux>>>(
-          indptr, indices, vals, x, y, p->heavy_rows_dev, p->n_heavy, p->slab_w / slab,
+      spmm_heavy_kernel<2><<<(unsigned)items, 32, heavy_smem_bytes<2>(), p->aux_heavy>>>(
+          indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
           p->feat_len);
     else
-      spmm_heavy_kernel<1><<<(unsigned)items, 32, heavy_smem_bytes<1>(), p->aux>>>(
-          indptr, indices, vals, x, y, p->heavy_rows_dev, p->n_heavy, p->slab_w / slab,
+      spmm_heavy_kernel<1><<<(unsigned)items, 32, heavy_smem_bytes<1>(), p->aux_heavy>>>(
+          indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
           p->feat_len);
     FG_CUDA_TRY(cudaGetLastError());
-    FG_CUDA_TRY(cudaEventRecord(p->join_ev, p->aux));
+    FG_CUDA_TRY(cudaEventRecord(p->join_heavy, p->aux_heavy));
   }
   if (p->n_light > 0) {
     switch (p->slab_w) {
@@ -519,7 +726,8 @@ extern "C" int fg_spmm_csr_f32(const fg_spmm_plan* p, const int32_t* indptr,
     }
     FG_CUDA_TRY(cudaGetLastError());
   }
-  if (p->n_heavy > 0) FG_CUDA_TRY(cudaStreamWaitEvent(st, p->join_ev, 0));
+  if (p->n_giant > 0) FG_CUDA_TRY(cudaStreamWaitEvent(st, p->join_giant, 0));
+  if (p->n_heavy > 0) FG_CUDA_TRY(cudaStreamWaitEvent(st, p->join_heavy, 0));
   return FG_OK;
 }
 

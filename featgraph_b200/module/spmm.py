@@ -180,6 +180,15 @@ class SpMMbase(object):
             ptr(self.out_tvm.torch), current_stream_handle(self._ctx)))
         return y_host
 
+    def device_status(self):
+        """Synchronise and return the status word of the plan's kernels: 0 when every
+        bounded device-side wait completed; raises FeatGraphError otherwise."""
+        if self._plan is None:
+            return 0
+        status = ctypes.c_int32(0)
+        _lib.check(_lib.load().fg_spmm_plan_status(self._plan, ctypes.byref(status)))
+        return int(status.value)
+
     def num_launches(self):
         """Kernels launched per ``run`` call."""
         return int(_lib.load().fg_spmm_plan_num_launches(self._plan)) if self._plan else 0

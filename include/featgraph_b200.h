@@ -59,6 +59,12 @@ int fg_spmm_plan_destroy(fg_spmm_plan* plan);
  * (python/featgraph/module/spmm.py:113-140). */
 int fg_spmm_plan_describe(const fg_spmm_plan* plan, char* buf, int64_t buf_len);
 
+/* Synchronises the plan's device and reads the status word its kernels write:
+ * 0 = fine; non-zero = a bounded wait inside the heavy-row kernel gave up (the
+ * call then also returns FG_ERR_CUDA and the affected rows were not written).
+ * The reference has no counterpart (TVM kernels have no device-side waits). */
+int fg_spmm_plan_status(const fg_spmm_plan* plan, int32_t* device_status);
+
 /* Number of kernels one fg_spmm_csr_f32 call launches with this plan. */
 int fg_spmm_plan_num_launches(const fg_spmm_plan* plan);
 

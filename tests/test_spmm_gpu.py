@@ -47,8 +47,27 @@ def test_feature_lengths_and_both_row_paths(oracle, feat_len, threshold):
     m, y = run_spmm(adj, x, {"heavy_row_threshold": threshold})
     assert np.array_equal(bits(oracle_spmm(oracle, adj, x)), bits(y))
     assert not y[[0, 17, 299]].any()
+    assert m.device_status() == 0
     if feat_len % 32 == 0 and threshold == 8:
-        assert m.num_launches() == 2          # light + heavy kernels both ran
+        assert m.num_launches() == 3          # light, heavy and giant kernels all ran
+
+
+@pytest.mark.parametrize("feat_len", [32, 64, 128])
+def test_giant_rows_wrap_the_stage_ring(oracle, feat_len):
+    # rows of 3000 / 2500 / 1900 nonzeros with a tiny threshold take the multi-warp giant
+    # kernel and go round its 16-slot ring several times; ragged last stages included
+    adj = random_csr(96, 3000, 0.02, seed=77, empty_rows=(1,)).tolil()
+    rs = np.random.RandomState(78)
+    adj[3, :] = rs.random_sample(3000).astype(np.float32) + 0.5
+    adj[40, :2500] = rs.random_sample(2500).astype(np.float32) + 0.5
+    adj[41, 1100:] = rs.random_sample(1900).astype(np.float32) + 0.5
+    adj = adj.tocsr().astype(np.float32)
+    x = features((3000, feat_len), seed=79)
+    m, y = run_spmm(adj, x, {"heavy_row_threshold": 8})
+    text = m.lower_to_ir([te.placeholder(x.shape)], {}, {"heavy_row_threshold": 8})
+    assert "giant: 0 rows" not in text and m.num_launches() == 3
+    assert m.device_status() == 0
+    assert np.array_equal(bits(oracle_spmm(oracle, adj, x)), bits(y))
 
 
 def test_weighted_values_are_not_fused(oracle):
@@ -164,6 +183,7 @@ def test_powerlaw_medium(oracle, feat_len):
     x = graphs.normal_features(20000, feat_len, graphs.FEAT_SEED, "cuda").cpu().numpy()
     m, y = run_spmm(adj, x)
     assert m.num_launches() == 2
+    assert m.device_status() == 0          # no bounded wait in the heavy kernel gave up
     assert np.array_equal(bits(oracle_spmm(oracle, adj, x)), bits(y))
 
 
@@ -235,4 +255,5 @@ def test_full_size_sampled_rows_against_oracle(full_graph, full_module, oracle):
     sub_val = g.vals[sel_t].cpu().numpy()
     want = oracle.spmm_csr_f32(sub_ptr, sub_idx, sub_val, x.cpu().numpy(), n_cols=g.n_cols)
     got = y1[torch.from_numpy(picks).cuda()].cpu().numpy()
+    assert m.device_status() == 0
     assert np.array_equal(bits(want), bits(got))

@@ -120,10 +120,8 @@ __device__ __forceinline__ void cp_async_arrive_on(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar))
                : "memory");
 }
-// Non-blocking test (test_wait, not try_wait: a try_wait that finds the phase
-// incomplete parks the thread for a scheduling quantum, which was measured to
-// cost about 1500 cycles per producer/consumer hand-over).
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+// Non-blocking test of a phase: true once the phase of `parity` has completed.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, unsigned parity) {
   unsigned done;
   asm volatile(
       "{\n"
@@ -136,13 +134,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
       : "memory");
   return done != 0;
 }
-// Waits for the phase of the given parity to complete, polling at most
-// `max_polls` times; returns false if it gave up (the caller records the error
-// and leaves instead of spinning forever).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity,
-                                                  unsigned max_polls) {
+// The same test, but the hardware may park the thread for a while when the phase
+// is not complete yet: gentler on the issue slots and the shared-memory pipe.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded waits: at most `max_polls` tests, then false (the caller records the
+// error and leaves instead of spinning forever).  spin = latency-critical waiter,
+// park = waiter that should stay out of the way.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, unsigned parity, unsigned max_polls) {
   for (unsigned i = 0; i < max_polls; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_park(uint64_t* bar, unsigned parity, unsigned max_polls) {
+  for (unsigned i = 0; i < max_polls; ++i)
+    if (mbar_try(bar, parity)) return true;
   return false;
 }
 

@@ -263,7 +263,8 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   heavy_store_row<VEC>(Y + (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
 }
 
-constexpr int kGtProducers = 7;   // producer warps per CTA
+constexpr int kGtWarps = 12;      // warps per CTA; warp 0 consumes, warps 4 and 8 retire
+constexpr int kGtProducers = 9;   // producer warps per CTA (the warps with id % 4 != 0)
 constexpr int kGtSlots = 16;      // ring of stages (power of two)
 constexpr int kGtQueue = 4;       // stages of column indices a producer holds in registers
 constexpr unsigned kGtMaxPolls = 1u << 24;  // bound of every barrier wait
@@ -277,6 +278,9 @@ constexpr int giant_smem_bytes() {
 }
 
 // One CTA of 1 consumer + kGtProducers producer warps per (giant row, slab).
+// Warps are dealt to the SM's four schedulers round-robin by id, so warps 4 and
+// 8 -- which would share the consumer's scheduler -- retire at once: the add
+// chain keeps a scheduler's issue slots to itself.
 //
 // The sum of one row is a dependent chain (CSR order, one accumulator per
 // feature), so the longest row bounds the whole SpMM.  A single warp cannot feed
@@ -289,7 +293,7 @@ constexpr int giant_smem_bytes() {
 // back through "empty" mbarriers.  Every barrier wait is a bounded poll; a wait
 // that gives up records a code in *status and the warp leaves.
 template <int VEC>
-__global__ void __launch_bounds__(32 * (kGtProducers + 1))
+__global__ void __launch_bounds__(32 * kGtWarps)
 spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
                   float* __restrict__ Y, const int* __restrict__ rows, int n_listed,
@@ -323,6 +327,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   }
   __syncthreads();
 
+  if (warp > 0 && (warp & 3) == 0) return;  // leave the consumer's scheduler alone
   if (warp > 0) {
     // ------------------------------------------------------------ producer --
     const int* ind = indices + beg;
@@ -330,7 +335,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     const int part = (lane % kLanesPerRow) * 4;
     const int first = lane / kLanesPerRow;
     const float* xbase = X + (size_t)sub * kSlab + part;
-    const int s_first = warp - 1;
+    const int s_first = warp - 1 - (warp >> 2);  // producer index 0 .. kGtProducers-1
     int idxq[kGtQueue];
 #pragma unroll
     for (int u = 0; u < kGtQueue; ++u) {
@@ -346,7 +351,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
           const int slot = s & (kGtSlots - 1);
           const unsigned round = (unsigned)(s / kGtSlots);
           // slot handed back by the consumer?  (passes at once in round 0)
-          ok = mbar_wait_bounded(&empty_bar[slot], (round & 1u) ^ 1u, kGtMaxPolls);
+          ok = mbar_wait_park(&empty_bar[slot], (round & 1u) ^ 1u, kGtMaxPolls);
           if (ok) {
             const int cnt = min(kHvEdges, deg - s * kHvEdges);
             const int my_idx = idxq[u];
@@ -371,16 +376,93 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   }
 
   // -------------------------------------------------------------- consumer --
+  // Software pipeline over the full stages: while the products of stage i are
+  // being added (the dependent chain), the segments of stage i+1 are read from
+  // shared memory and multiplied into a second register set.  A stage's slot is
+  // handed back as soon as its products sit in registers.
   float acc_a = 0.f, acc_b = 0.f;
+  float pa[kHvEdges], pb[kHvEdges], qa[kHvEdges], qb[kHvEdges];
+  const int n_full = deg / kHvEdges;
   bool ok = true;
-  for (int i = 0; i < n_stages; ++i) {
-    const int slot = i & (kGtSlots - 1);
-    ok = mbar_wait_bounded(&full_bar[slot], (unsigned)(i / kGtSlots) & 1u, kGtMaxPolls);
-    if (!ok) break;
-    heavy_consume_stage<VEC>(xs[slot], val_s[slot], min(kHvEdges, deg - i * kHvEdges), lane,
-                             acc_a, acc_b);
+  auto wait_stage = [&](int i) {
+    return mbar_wait_spin(&full_bar[i & (kGtSlots - 1)], (unsigned)(i / kGtSlots) & 1u,
+                          kGtMaxPolls);
+  };
+  auto release_stage = [&](int i) {
     __syncwarp();  // every lane has read the slot
-    if (lane == 0) mbar_arrive(&empty_bar[slot]);
+    if (lane == 0) mbar_arrive(&empty_bar[i & (kGtSlots - 1)]);
+  };
+#define FG_GIANT_PRODUCTS(i, A, B)                                                        \
+  do {                                                                                    \
+    const float(*xt)[kSlab] = xs[(i) & (kGtSlots - 1)];                                   \
+    const float* vt = val_s[(i) & (kGtSlots - 1)];                                        \
+    _Pragma("unroll") for (int e4 = 0; e4 < kHvEdges; e4 += 4) {                          \
+      const float4 v4 = *reinterpret_cast<const float4*>(vt + e4);                        \
+      const float vv[4] = {v4.x, v4.y, v4.z, v4.w};                                       \
+      _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                     \
+        if (VEC == 2) {                                                                   \
+          const float2 xv = *reinterpret_cast<const float2*>(&xt[e4 + q][lane * 2]);      \
+          A[e4 + q] = __fmul_rn(vv[q], xv.x);                                             \
+          B[e4 + q] = __fmul_rn(vv[q], xv.y);                                             \
+        } else {                                                                          \
+          A[e4 + q] = __fmul_rn(vv[q], xt[e4 + q][lane]);                                 \
+          B[e4 + q] = 0.f;                                                                \
+        }                                                                                 \
+      }                                                                                   \
+    }                                                                                     \
+  } while (0)
+#define FG_GIANT_CHAIN(A, B)                                                              \
+  do {                                                                                    \
+    _Pragma("unroll") for (int e = 0; e < kHvEdges; ++e) {                                \
+      acc_a = __fadd_rn(acc_a, A[e]);                                                     \
+      if (VEC == 2) acc_b = __fadd_rn(acc_b, B[e]);                                       \
+    }                                                                                     \
+  } while (0)
+
+  // products(i+1) and chain(i) share one basic block so that the compiler
+  // interleaves the shared-memory reads and multiplies with the add chain.
+  if (n_full > 0) {
+    ok = wait_stage(0);
+    if (ok) {
+      FG_GIANT_PRODUCTS(0, pa, pb);
+      release_stage(0);
+    }
+    int i = 0;
+    while (ok && i + 2 < n_full) {
+      ok = wait_stage(i + 1);
+      if (!ok) break;
+      FG_GIANT_PRODUCTS(i + 1, qa, qb);
+      FG_GIANT_CHAIN(pa, pb);
+      release_stage(i + 1);
+      ok = wait_stage(i + 2);
+      if (!ok) break;
+      FG_GIANT_PRODUCTS(i + 2, pa, pb);
+      FG_GIANT_CHAIN(qa, qb);
+      release_stage(i + 2);
+      i += 2;
+    }
+    // stage i is in (pa, pb); at most one more full stage follows
+    if (ok && i + 1 < n_full) {
+      ok = wait_stage(i + 1);
+      if (ok) {
+        FG_GIANT_PRODUCTS(i + 1, qa, qb);
+        FG_GIANT_CHAIN(pa, pb);
+        release_stage(i + 1);
+        FG_GIANT_CHAIN(qa, qb);
+      }
+    } else if (ok) {
+      FG_GIANT_CHAIN(pa, pb);
+    }
+  }
+#undef FG_GIANT_PRODUCTS
+#undef FG_GIANT_CHAIN
+  if (ok && n_full < n_stages) {  // the ragged last stage
+    ok = wait_stage(n_full);
+    if (ok) {
+      heavy_consume_stage<VEC>(xs[n_full & (kGtSlots - 1)], val_s[n_full & (kGtSlots - 1)],
+                               deg - n_full * kHvEdges, lane, acc_a, acc_b);
+      release_stage(n_full);
+    }
   }
   if (!ok) {
     if (lane == 0) atomicExch(status, kGtErrConsumerTimeout);
@@ -630,7 +712,7 @@ extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t b
              (light_items + 256 / G - 1) / (256 / G), p->n_heavy, p->giant_threshold,
              (long long)p->heavy_nnz, p->heavy_vec, (long long)p->n_heavy * hv_slabs, kHvXSlots,
              p->n_giant, (long long)p->giant_nnz, p->heavy_vec, (long long)p->n_giant * hv_slabs,
-             32 * (kGtProducers + 1), kGtProducers, kGtSlots);
+             32 * kGtWarps, kGtProducers, kGtSlots);
   } else {
     snprintf(buf, (size_t)buf_len,
              "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d | spmm_generic_kernel "
@@ -691,7 +773,7 @@ extern "C" int fg_spmm_csr_f32(const fg_spmm_plan* p, const int32_t* indptr,
   if (p->n_giant > 0) {
     FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_giant, p->fork_ev, 0));
     const unsigned grid = (unsigned)(p->n_giant * hv_slabs);
-    const unsigned threads = 32 * (kGtProducers + 1);
+    const unsigned threads = 32 * kGtWarps;
     if (p->heavy_vec == 2)
       spmm_giant_kernel<2><<<grid, threads, giant_smem_bytes<2>(), p->aux_giant>>>(
           indptr, indices, vals, x, y, p->rows_dev, p->n_giant, p->slab_w / slab, p->feat_len,

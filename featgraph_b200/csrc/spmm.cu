@@ -267,7 +267,11 @@ constexpr int kGtWarps = 12;      // warps per CTA; warp 0 consumes, warps 4 and
 constexpr int kGtProducers = 9;   // producer warps per CTA (the warps with id % 4 != 0)
 constexpr int kGtSlots = 16;      // ring of stages (power of two)
 constexpr int kGtQueue = 4;       // stages of column indices a producer holds in registers
-constexpr unsigned kGtMaxPolls = 1u << 24;  // bound of every barrier wait
+constexpr unsigned kGtMaxPolls = 1u << 20;  // bound of every barrier wait
+// A parity wait tells the current phase from the previous one only.  A producer's
+// consecutive stages are kGtProducers apart; were that more than the ring size it
+// would skip a round of a slot and its wait would pass one phase too early.
+static_assert(kGtProducers <= kGtSlots, "a producer may not skip a round of a slot");
 constexpr int kGtErrProducerTimeout = 1, kGtErrConsumerTimeout = 2;
 
 template <int VEC>

@@ -24,10 +24,14 @@ namespace fg {
 constexpr int kSdChunk = 32;             // floats per row per stage
 constexpr int kSdPitch = kSdChunk + 4;   // smem row pitch (floats): conflict-free LDS.128
 constexpr int kSdWarps = 4;              // warps per CTA
-// one stage: src segments of 32 edges, dst segments of up to 32 distinct rows, 32 slot ids
-constexpr int kSdStageFloats = 2 * 32 * kSdPitch + 32;
-constexpr int kSdWarpFloats = 2 * kSdStageFloats;  // double buffered
+constexpr int kSdStages = 3;             // stages per warp: two in flight, one being consumed
+constexpr int kSdDstSlots = 8;           // distinct dst rows a stage can hold
+// one stage: src segments of 32 edges, dst segments of up to 8 distinct rows, then
+// 32 per-lane words (slot id, or the row itself) and the 8 row ids of the slots
+constexpr int kSdStageFloats = 32 * kSdPitch + kSdDstSlots * kSdPitch + 32 + kSdDstSlots;
+constexpr int kSdWarpFloats = kSdStages * kSdStageFloats;
 constexpr int kSdSmemBytes = kSdWarps * kSdWarpFloats * 4;
+static_assert(kSdStageFloats % 4 == 0, "stages stay 16-byte aligned");
 
 // HEADS_PER_CHUNK: number of heads that end inside one 32-float chunk
 // (1, 2, 4 or 8 <=> D = 32, 16, 8, 4), or 0 when D is a multiple of 32 larger
@@ -54,9 +58,11 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
   // State of the tile being issued: one edge per lane, and the tile's runs of
   // equal row index.  Edge lists sorted by row repeat dst[row] for hundreds of
   // consecutive edges; each distinct run is staged once ("slot") and the lanes of
-  // the run read it back as a shared-memory broadcast.
-  int r_iss = 0, c_iss = 0, slot_iss = 0, n_slots = 1;
-  unsigned run_heads = 1u;
+  // the run read it back as a shared-memory broadcast.  A tile with more than
+  // kSdDstSlots runs (an unsorted list, or very short rows) stages no dst rows:
+  // its lanes read their dst segments straight from global memory instead.
+  int r_iss = 0, c_iss = 0, word_iss = 0, n_slots = 1;
+  bool head_iss = false;
   // Indices of the tile after the one being issued, fetched a whole tile ahead
   // so that their DRAM latency never stalls the copy pipeline.
   int r_ahead = 0, c_ahead = 0;
@@ -74,9 +80,12 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
     c_iss = c_ahead;
     fetch_indices(t + 1);
     const int r_left = __shfl_up_sync(kFull, r_iss, 1);
-    run_heads = __ballot_sync(kFull, lane == 0 || r_iss != r_left);
-    slot_iss = __popc(run_heads & (0xffffffffu >> (31 - lane))) - 1;
+    head_iss = lane == 0 || r_iss != r_left;
+    const unsigned run_heads = __ballot_sync(kFull, head_iss);
     n_slots = __popc(run_heads);
+    const int slot = __popc(run_heads & (0xffffffffu >> (31 - lane))) - 1;
+    // per-lane word: slot id (>= 0), or -1 - row when the tile reads dst directly
+    word_iss = n_slots <= kSdDstSlots ? slot : -1 - r_iss;
   };
   // Stage (tile t_iss, chunk ch_iss) into buffer `buf`.
   int t_iss = 0, ch_iss = 0;
@@ -84,20 +93,28 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
     if (ch_iss == 0) begin_tile(t_iss);
     float* sbuf = wbuf + buf * kSdStageFloats;
     float* dbuf = sbuf + 32 * kSdPitch;
-    reinterpret_cast<int*>(dbuf + 32 * kSdPitch)[lane] = slot_iss;
+    int* words = reinterpret_cast<int*>(dbuf + kSdDstSlots * kSdPitch);
+    int* slot_rows = words + 32;
+    const bool staged = n_slots <= kSdDstSlots;
+    words[lane] = word_iss;
+    if (staged && head_iss) slot_rows[word_iss] = r_iss;
+    __syncwarp();
     const int part = (lane & 7) * 4;
     const size_t foff = (size_t)ch_iss * kSdChunk + part;
+    const float* sp = src + foff;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const int e = (lane >> 3) + 4 * k;
       const int c = __shfl_sync(kFull, c_iss, e);
-      cp_async16_cg(sbuf + e * kSdPitch + part, src + (size_t)c * F + foff);
+      cp_async16_ca(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
     }
-    for (int k = 0; 4 * k < n_slots; ++k) {
-      const int slot = (lane >> 3) + 4 * k;
-      const unsigned head = __fns(run_heads, 0, min(slot, n_slots - 1) + 1);
-      const int r = __shfl_sync(kFull, r_iss, head);
-      if (slot < n_slots) cp_async16_ca(dbuf + slot * kSdPitch + part, dst + (size_t)r * F + foff);
+    if (staged) {
+#pragma unroll
+      for (int k = 0; k < kSdDstSlots / 4; ++k) {
+        const int slot = (lane >> 3) + 4 * k;
+        if (slot < n_slots)
+          cp_async16_ca(dbuf + slot * kSdPitch + part, dst + (size_t)slot_rows[slot] * F + foff);
+      }
     }
     if (++ch_iss == n_chunks) {
       ch_iss = 0;
@@ -108,19 +125,26 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
   fetch_indices(0);
   issue(0);
   cp_async_commit();
+  if (total > 1) issue(1);
+  cp_async_commit();
   float acc = 0.f;
-  int head = 0, chunk = 0;
+  int head = 0, chunk = 0, buf = 0, buf_issue = 2;
   long long e = tile0 * 32 + lane;
   for (int it = 0; it < total; ++it) {
-    if (it + 1 < total) issue((it + 1) & 1);
+    if (it + 2 < total) issue(buf_issue);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<2>();
     __syncwarp();
 
-    const float* stage = wbuf + (it & 1) * kSdStageFloats;
-    const int slot = reinterpret_cast<const int*>(stage + 64 * kSdPitch)[lane];
+    const float* stage = wbuf + buf * kSdStageFloats;
+    const int word = reinterpret_cast<const int*>(stage + (32 + kSdDstSlots) * kSdPitch)[lane];
     const float4* s4 = reinterpret_cast<const float4*>(stage + lane * kSdPitch);
-    const float4* d4 = reinterpret_cast<const float4*>(stage + (32 + slot) * kSdPitch);
+    // word >= 0: this lane's dst segment is slot `word` of the stage; otherwise it
+    // is row -1 - word of dst in global memory (uniform across the warp)
+    const float4* d4 =
+        word >= 0 ? reinterpret_cast<const float4*>(stage + (32 + word) * kSdPitch)
+                  : reinterpret_cast<const float4*>(dst + (size_t)(-1 - word) * F +
+                                                    (size_t)chunk * kSdChunk);
 #pragma unroll
     for (int q = 0; q < kSdChunk / 4; ++q) {
       const float4 a = s4[q];
@@ -147,6 +171,8 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
       acc = 0.f;
       e += 32;
     }
+    buf = buf == kSdStages - 1 ? 0 : buf + 1;
+    buf_issue = buf_issue == kSdStages - 1 ? 0 : buf_issue + 1;
     __syncwarp();  // every lane is done with this buffer before it is refilled
   }
   cp_async_wait<0>();
@@ -168,7 +194,7 @@ sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
   out[i] = acc;
 }
 
-constexpr int kSdTilesPerWarp = 8;
+constexpr int kSdTilesPerWarp = 16;
 
 // 0 -> generic kernel; otherwise HEADS_PER_CHUNK + 1 of the tile kernel.
 static int sddmm_variant(int F, int H) {
@@ -206,7 +232,7 @@ extern "C" int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_head
     const long long per_cta = (long long)kSdWarps * kSdTilesPerWarp;
     snprintf(buf, (size_t)buf_len,
              "sddmm_coo_f32 nnz=%lld feat_len=%d heads=%d | sddmm_tile_kernel<heads_per_chunk=%d> "
-             "grid=%lld x %d thr, %d B smem, 32 edges x 32 floats per stage, double buffered",
+             "grid=%lld x %d thr, %d B smem, 32 edges x 32 floats per stage, 3-stage ring",
              (long long)nnz, feat_len, num_heads, v - 1, (long long)((tiles + per_cta - 1) / per_cta),
              kSdWarps * 32, kSdSmemBytes);
   }

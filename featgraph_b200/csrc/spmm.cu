@@ -7,17 +7,22 @@
 // parallelism is across rows and across features, never across one row's
 // nonzeros.
 //
-// Rows are binned by degree on the host (plan):
-//   * light rows  -> spmm_light_kernel: a group of G = W/4 lanes owns one
-//                    (row, W-float feature slab); float4 gathers, 8 in flight
-//                    per lane; rows are served in descending degree so the
-//                    groups of a warp finish together.
-//   * heavy rows  -> spmm_heavy_kernel: one warp owns one (row, 32-float
-//                    slab); indices/values and the gathered X segments are
-//                    staged through shared memory with cp.async rings, which
-//                    decouples the sequential add chain from the gather
-//                    latency.  Launched on an auxiliary stream so the long
-//                    rows overlap the light kernel.
+// Rows are sorted by degree on the host (plan) and split into three classes,
+// each with its own kernel, launched on three streams so that they overlap:
+//   * light rows (deg <= 2048) -> spmm_light_kernel: a group of G = W/4 lanes
+//       owns one (row, W-float feature slab); float4 gathers straight into
+//       registers, 8 in flight per lane, index/value tile fetched one iteration
+//       ahead; rows are served in descending degree so that the groups of a
+//       warp finish together.
+//   * heavy rows -> spmm_heavy_kernel: one warp owns one (row, 32- or 64-float
+//       slab); indices/values and the gathered X segments are staged through
+//       shared memory with cp.async rings, which takes the gather latency off
+//       the sequential add chain.
+//   * giant rows (deg > 32768, at most one CTA per SM) -> spmm_giant_kernel: a
+//       consumer warp adds in order while nine producer warps gather, handing
+//       stages over through mbarriers.  The longest row bounds the whole call
+//       (its sum is one dependent chain) and a single warp cannot keep enough
+//       copies in flight to feed that chain.
 //   * anything the vector paths cannot take (feat_len not a multiple of 32,
 //     unaligned pointers) -> spmm_generic_kernel, one warp per row.
 #include <algorithm>

@@ -1,0 +1,131 @@
+"""Command-line benchmark with the flags of the reference's scripts
+(benchmark/bench_vanilla_spmm.py:71-84, bench_vanilla_sddmm.py:77-90):
+
+    python -m featgraph_b200.bench_cli --kernel spmm  --dataset reddit_csr_float32.npz --feat-len 64 --target cuda
+    python -m featgraph_b200.bench_cli --kernel sddmm --synthetic powerlaw --feat-len 128
+    python -m featgraph_b200.bench_cli --kernel sddmm --synthetic powerlaw --heads 8 --head-dim 32
+    torchrun --nproc-per-node 8 -m featgraph_b200.bench_cli --kernel spmm --synthetic rmat --feat-len 64
+
+``--dataset`` is a scipy ``save_npz`` file (CSR for SpMM, COO for SDDMM), as the reference's
+download script writes them; ``--synthetic`` generates one of the seeded graphs of
+``featgraph_b200.graphs`` on the GPU instead.  The reference's scripts sweep TVM schedule
+parameters and print the mean of 5 runs; the kernels here have no such parameters, so one
+JSON line per feature length is printed: mean milliseconds over ``--num-runs`` launches
+(kernel only, inputs resident, as ``measure_average_time``), GFLOP/s and algorithmic GB/s.
+Under torchrun the graph is sharded over the ranks and the all-gather is inside the time.
+"""
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import graphs
+from .distributed import ShardedSDDMM, ShardedSpMM
+
+NOMINAL_HBM_GBS = 8000.0
+
+
+def _load_graph(args, device):
+    if args.dataset:
+        import scipy.sparse as sp
+        m = sp.load_npz(args.dataset)
+        csr = m.tocsr().astype(np.float32)
+        csr.sort_indices()
+        return graphs.CSRGraph(csr.shape[0], csr.shape[1],
+                               torch.from_numpy(csr.indptr.astype(np.int32)).to(device),
+                               torch.from_numpy(csr.indices.astype(np.int32)).to(device),
+                               torch.from_numpy(csr.data).to(device)), "file:" + args.dataset
+    if args.synthetic == "powerlaw":
+        g = graphs.powerlaw_graph(n=args.vertices or graphs.REDDIT_NUM_VERTICES,
+                                  nnz_target=args.edges or graphs.REDDIT_NUM_EDGES, device=device)
+    elif args.synthetic == "rmat":
+        g = graphs.rmat_graph(scale=args.scale, edge_draws=args.edges or (1 << (args.scale + 4)),
+                              device=device)
+    else:
+        g = graphs.regular_graph(n=args.vertices or 65536, device=device)
+    return g, "synthetic:" + args.synthetic
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--kernel", choices=["spmm", "sddmm"], default="spmm")
+    ap.add_argument("--dataset", type=str, default=None,
+                    help="adjacency matrix stored as a scipy npz file")
+    ap.add_argument("--synthetic", choices=["powerlaw", "rmat", "regular"], default="powerlaw")
+    ap.add_argument("--feat-len", type=str, default="128",
+                    help="feature length, or a comma-separated list")
+    ap.add_argument("--heads", type=int, default=1, help="SDDMM heads (feat-len = heads x head-dim)")
+    ap.add_argument("--head-dim", type=int, default=0)
+    ap.add_argument("--target", choices=["cuda", "x86"], default="cuda")
+    ap.add_argument("--num-runs", type=int, default=20)
+    ap.add_argument("--vertices", type=int, default=0)
+    ap.add_argument("--edges", type=int, default=0)
+    ap.add_argument("--scale", type=int, default=24, help="R-MAT scale (2**scale vertices)")
+    args = ap.parse_args(argv)
+    if args.target != "cuda":
+        raise SystemExit("this backend ships the cuda target only (no x86 code path)")
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    g, source = _load_graph(args, device)
+    n, nnz = g.n_rows, g.nnz
+    if args.heads > 1:
+        feat_lens = [args.heads * (args.head_dim or 16)]
+    else:
+        feat_lens = [int(f) for f in args.feat_len.split(",")]
+    adj = g.to_scipy() if args.kernel == "spmm" else None
+    rows = g.coo_rows() if args.kernel == "sddmm" else None
+
+    for f in feat_lens:
+        shape = (args.heads, f // args.heads) if args.heads > 1 else (f,)
+        x = graphs.normal_features(g.n_cols, shape, graphs.FEAT_SEED, device)
+        if args.kernel == "spmm":
+            op = ShardedSpMM(adj, f, device)
+            call = lambda: op.run(x)                       # noqa: E731
+            alg = 4 * (n + 1) + 8 * nnz + 4 * nnz * f + 4 * n * f
+        else:
+            y2 = graphs.normal_features(g.n_rows, shape, graphs.FEAT2_SEED, device)
+            op = ShardedSDDMM(rows, g.indices, n, g.n_cols, shape, device)
+            call = lambda: op.run(x, y2)                   # noqa: E731
+            alg = 8 * nnz + 8 * nnz * f + 4 * nnz * args.heads
+        for _ in range(3):
+            call()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.num_runs):
+            call()
+        t1.record()
+        torch.cuda.synchronize(device)
+        ms = torch.tensor([t0.elapsed_time(t1) / args.num_runs], device=device,
+                          dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        ms = float(ms)
+        if rank == 0:
+            print(json.dumps({
+                "kernel": args.kernel, "graph": source, "rows": n, "nnz": nnz, "feat_len": f,
+                "heads": args.heads, "n_gpus": world, "num_runs": args.num_runs,
+                "ms": round(ms, 4), "gflops": round(2.0 * nnz * f / ms / 1e6, 1),
+                "alg_gbs": round(alg / ms / 1e6, 1),
+                "frac_of_8TBs": round(alg / ms / 1e6 / NOMINAL_HBM_GBS, 4),
+                "degree": g.degree_stats()}), flush=True)
+        del op, x
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -106,7 +106,7 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
     for (int k = 0; k < 8; ++k) {
       const int e = (lane >> 3) + 4 * k;
       const int c = __shfl_sync(kFull, c_iss, e);
-      cp_async16_ca(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
+      cp_async16_cg(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
     }
     if (staged) {
 #pragma unroll

@@ -6,11 +6,11 @@
 // unscheduled reduction (python/featgraph/op/vanilla_sddmm.py:43-47, 66-74) --
 // so results are bit-equal to a sequential loop.
 //
-// sddmm_tile_kernel: each warp owns 32 consecutive edges per tile.  The two
-// gathered feature rows of every edge are staged, 32 floats at a time, into
-// shared memory with 16-byte cp.async copies in which 8 lanes read one 128-byte
-// row segment (coalesced gathers); the copy of the next (tile, chunk) overlaps
-// the arithmetic of the current one.  Each lane then walks ITS edge's two
+// sddmm_tile_kernel: each warp owns 32 consecutive edges per tile.  The
+// gathered feature rows are staged, 32 floats at a time, into shared memory with
+// 16-byte cp.async copies in which 8 lanes read one 128-byte row segment
+// (coalesced gathers); latency is hidden by the 36 warps an SM holds, not by a
+// ring per warp.  Each lane then walks ITS edge's two
 // segments with float4 shared-memory loads (row pitch 36 floats, conflict
 // free) and adds the products in order.  Runs of consecutive edges with the
 // same row (the normal case for a row-sorted COO list) stage dst[row] once per
@@ -23,8 +23,12 @@ namespace fg {
 
 constexpr int kSdChunk = 32;             // floats per row per stage
 constexpr int kSdPitch = kSdChunk + 4;   // smem row pitch (floats): conflict-free LDS.128
-constexpr int kSdWarps = 4;              // warps per CTA
-constexpr int kSdStages = 3;             // stages per warp: two in flight, one being consumed
+constexpr int kSdWarps = 6;              // warps per CTA
+// Stages per warp.  One: a warp copies a stage, waits, consumes it.  Measured on B200
+// (114.6 M edges, feat_len 64): 1 stage x 36 warps/SM 2.76 ms, 2 x 18 3.21 ms, 3 x 12
+// 3.94 ms -- a warp keeps only a few cp.async copies outstanding however deep its
+// ring, so shared memory is better spent on more warps than on deeper rings.
+constexpr int kSdStages = 1;
 constexpr int kSdDstSlots = 8;           // distinct dst rows a stage can hold
 // one stage: src segments of 32 edges, dst segments of up to 8 distinct rows, then
 // 32 per-lane words (slot id, or the row itself) and the 8 row ids of the slots
@@ -33,10 +37,13 @@ constexpr int kSdWarpFloats = kSdStages * kSdStageFloats;
 constexpr int kSdSmemBytes = kSdWarps * kSdWarpFloats * 4;
 static_assert(kSdStageFloats % 4 == 0, "stages stay 16-byte aligned");
 
-// HEADS_PER_CHUNK: number of heads that end inside one 32-float chunk
-// (1, 2, 4 or 8 <=> D = 32, 16, 8, 4), or 0 when D is a multiple of 32 larger
-// than 32 (heads end only at chunk boundaries).
-template <int HEADS_PER_CHUNK>
+constexpr int kSdLanesPerSeg = kSdChunk / 4;          // 16-byte copies per row segment
+constexpr int kSdRowsPerCopy = 32 / kSdLanesPerSeg;   // segments one warp-wide copy covers
+
+// HEAD_DIM: the head size D when a head ends inside a chunk (D = 4, 8, ... up to
+// the chunk size), or 0 when D is a larger multiple of the chunk (heads end only at
+// chunk boundaries).
+template <int HEAD_DIM>
 __global__ void __launch_bounds__(kSdWarps * 32)
 sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
                   const float* __restrict__ src, const float* __restrict__ dst,
@@ -53,7 +60,7 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
   const int my_tiles = (int)min((long long)tiles_per_warp, n_tiles - tile0);
   const int n_chunks = F / kSdChunk;
   const int total = my_tiles * n_chunks;
-  const int chunks_per_head = HEADS_PER_CHUNK == 0 ? (F / H) / kSdChunk : 1;
+  const int chunks_per_head = HEAD_DIM == 0 ? (F / H) / kSdChunk : 1;
 
   // State of the tile being issued: one edge per lane, and the tile's runs of
   // equal row index.  Edge lists sorted by row repeat dst[row] for hundreds of
@@ -99,19 +106,19 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
     words[lane] = word_iss;
     if (staged && head_iss) slot_rows[word_iss] = r_iss;
     __syncwarp();
-    const int part = (lane & 7) * 4;
+    const int part = (lane % kSdLanesPerSeg) * 4;
     const size_t foff = (size_t)ch_iss * kSdChunk + part;
     const float* sp = src + foff;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const int e = (lane >> 3) + 4 * k;
+    for (int k = 0; k < 32 / kSdRowsPerCopy; ++k) {
+      const int e = lane / kSdLanesPerSeg + kSdRowsPerCopy * k;
       const int c = __shfl_sync(kFull, c_iss, e);
       cp_async16_cg(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
     }
     if (staged) {
 #pragma unroll
-      for (int k = 0; k < kSdDstSlots / 4; ++k) {
-        const int slot = (lane >> 3) + 4 * k;
+      for (int k = 0; k < (kSdDstSlots + kSdRowsPerCopy - 1) / kSdRowsPerCopy; ++k) {
+        const int slot = lane / kSdLanesPerSeg + kSdRowsPerCopy * k;
         if (slot < n_slots)
           cp_async16_ca(dbuf + slot * kSdPitch + part, dst + (size_t)slot_rows[slot] * F + foff);
       }
@@ -123,17 +130,18 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
   };
 
   fetch_indices(0);
-  issue(0);
-  cp_async_commit();
-  if (total > 1) issue(1);
-  cp_async_commit();
+#pragma unroll
+  for (int p = 0; p < kSdStages - 1; ++p) {
+    if (p < total) issue(p);
+    cp_async_commit();
+  }
   float acc = 0.f;
-  int head = 0, chunk = 0, buf = 0, buf_issue = 2;
+  int head = 0, chunk = 0, buf = 0, buf_issue = kSdStages - 1;
   long long e = tile0 * 32 + lane;
   for (int it = 0; it < total; ++it) {
-    if (it + 2 < total) issue(buf_issue);
+    if (it + kSdStages - 1 < total) issue(buf_issue);
     cp_async_commit();
-    cp_async_wait<2>();
+    cp_async_wait<kSdStages - 1>();
     __syncwarp();
 
     const float* stage = wbuf + buf * kSdStageFloats;
@@ -153,14 +161,14 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
       acc = mul_then_add(acc, a.y, b.y);
       acc = mul_then_add(acc, a.z, b.z);
       acc = mul_then_add(acc, a.w, b.w);
-      if (HEADS_PER_CHUNK > 0 && ((q + 1) % (8 / (HEADS_PER_CHUNK > 0 ? HEADS_PER_CHUNK : 1))) == 0) {
+      if (HEAD_DIM > 0 && ((q + 1) * 4) % (HEAD_DIM > 0 ? HEAD_DIM : 4) == 0) {
         if (e < nnz) out[(size_t)e * H + head] = acc;
         ++head;
         acc = 0.f;
       }
     }
     ++chunk;
-    if (HEADS_PER_CHUNK == 0 && chunk % chunks_per_head == 0) {
+    if (HEAD_DIM == 0 && chunk % chunks_per_head == 0) {
       if (e < nnz) out[(size_t)e * H + head] = acc;
       ++head;
       acc = 0.f;
@@ -196,15 +204,13 @@ sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
 
 constexpr int kSdTilesPerWarp = 16;
 
-// 0 -> generic kernel; otherwise HEADS_PER_CHUNK + 1 of the tile kernel.
+// -1 -> generic kernel; otherwise the HEAD_DIM template argument of the tile kernel.
 static int sddmm_variant(int F, int H) {
-  if (F % kSdChunk != 0 || F % H != 0) return 0;
+  if (F % kSdChunk != 0 || F % H != 0) return -1;
   const int D = F / H;
-  if (D % kSdChunk == 0) return D == kSdChunk ? 2 : 1;  // hpc 1 or 0
-  if (D == 16) return 3;
-  if (D == 8) return 5;
-  if (D == 4) return 9;
-  return 0;
+  if (D % kSdChunk == 0) return D == kSdChunk ? kSdChunk : 0;
+  if (D == 4 || D == 8 || (D == 16 && kSdChunk > 16)) return D;
+  return -1;
 }
 
 }  // namespace fg
@@ -222,7 +228,7 @@ extern "C" int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_head
   if (num_heads <= 0 || feat_len <= 0 || feat_len % num_heads != 0)
     return fail(FG_ERR_INVALID_ARGUMENT, "feat_len must be a positive multiple of num_heads");
   const int v = sddmm_variant(feat_len, num_heads);
-  if (v == 0) {
+  if (v < 0) {
     snprintf(buf, (size_t)buf_len,
              "sddmm_coo_f32 nnz=%lld feat_len=%d heads=%d | sddmm_generic_kernel grid=%lld x 256 thr",
              (long long)nnz, feat_len, num_heads,
@@ -231,10 +237,10 @@ extern "C" int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_head
     const long long tiles = (nnz + 31) / 32;
     const long long per_cta = (long long)kSdWarps * kSdTilesPerWarp;
     snprintf(buf, (size_t)buf_len,
-             "sddmm_coo_f32 nnz=%lld feat_len=%d heads=%d | sddmm_tile_kernel<heads_per_chunk=%d> "
-             "grid=%lld x %d thr, %d B smem, 32 edges x 32 floats per stage, 3-stage ring",
-             (long long)nnz, feat_len, num_heads, v - 1, (long long)((tiles + per_cta - 1) / per_cta),
-             kSdWarps * 32, kSdSmemBytes);
+             "sddmm_coo_f32 nnz=%lld feat_len=%d heads=%d | sddmm_tile_kernel<head_dim=%d> "
+             "grid=%lld x %d thr, %d B smem, 32 edges x %d floats per stage, %d-stage ring per warp",
+             (long long)nnz, feat_len, num_heads, v, (long long)((tiles + per_cta - 1) / per_cta),
+             kSdWarps * 32, kSdSmemBytes, kSdChunk, kSdStages);
   }
   return FG_OK;
 }
@@ -263,8 +269,8 @@ extern "C" int fg_sddmm_coo_f32(const int32_t* row, const int32_t* col, const fl
 
   const bool aligned = (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(dst) % 16 == 0);
-  const int variant = aligned ? sddmm_variant(feat_len, num_heads) : 0;
-  if (variant == 0) {
+  const int variant = aligned ? sddmm_variant(feat_len, num_heads) : -1;
+  if (variant < 0) {
     const long long n_out = (long long)nnz * num_heads;
     const long long grid = (n_out + 255) / 256;
     if (grid >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "output too large for the generic kernel");
@@ -290,12 +296,12 @@ extern "C" int fg_sddmm_coo_f32(const int32_t* row, const int32_t* col, const fl
     sddmm_tile_kernel<HPC><<<(unsigned)grid, kSdWarps * 32, kSdSmemBytes, st>>>(             \
         row, col, src, dst, out, nnz, feat_len, num_heads, kSdTilesPerWarp);                 \
   } while (0)
-  switch (variant - 1) {
+  switch (variant) {
     case 0: FG_SD_LAUNCH(0); break;
-    case 1: FG_SD_LAUNCH(1); break;
-    case 2: FG_SD_LAUNCH(2); break;
     case 4: FG_SD_LAUNCH(4); break;
-    default: FG_SD_LAUNCH(8); break;
+    case 8: FG_SD_LAUNCH(8); break;
+    case 16: FG_SD_LAUNCH(16); break;
+    default: FG_SD_LAUNCH(32); break;
   }
 #undef FG_SD_LAUNCH
   FG_CUDA_TRY(cudaGetLastError());

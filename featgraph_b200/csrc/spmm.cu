@@ -117,9 +117,9 @@ spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
 }
 
 constexpr int kHvEdges = 32;    // nonzeros per stage
-constexpr int kHvXSlots = 4;    // ring of gathered X segments (power of two)
+constexpr int kHvXSlots = 2;    // ring of gathered X segments (power of two)
 constexpr int kHvDist = kHvXSlots - 1;  // stages of gathers in flight
-constexpr int kHvISlots = 8;    // ring of index/value tiles, >= 2 * kHvDist + 1
+constexpr int kHvISlots = 4;    // ring of index/value tiles, >= 2 * kHvDist + 1
 
 template <int VEC>
 constexpr int heavy_smem_bytes() {

@@ -38,6 +38,9 @@ FEAT = 64
 METRIC = "spmm_plus_sddmm_fp32_feat64_gflops"
 UNIT = "GFLOP/s"
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload, from one
+# ncu capture (profiles/bench_full_size_launch_list_and_dram.md); other sizes report null.
+NCU_TRAFFIC_BYTES = {"spmm": 1574.9e6 + 64.7e6, "sddmm": 1530.0e6 + 451.8e6}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -322,6 +325,12 @@ def run_gpu(args):
         local_sddmm_bytes = sddmm_alg_bytes(sddmm.edge_hi - sddmm.edge_lo, FEAT)
         spmm_ms, sddmm_ms = float(phase_ms[0]), float(phase_ms[2])
 
+        default_size = (world == 1 and n == graphs.REDDIT_NUM_VERTICES
+                        and abs(nnz - graphs.REDDIT_NUM_EDGES) < 0.01 * graphs.REDDIT_NUM_EDGES)
+
+        def traffic(kernel):
+            return int(NCU_TRAFFIC_BYTES[kernel]) if default_size else None
+
         def roof(alg_bytes, ms, traffic):
             ach = alg_bytes / (ms * 1e-3) / 1e9
             return {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s",
@@ -331,12 +340,13 @@ def run_gpu(args):
                     "traffic": traffic}
 
         kernels = {
-            "spmm": dict(roof(local_spmm_bytes, spmm_ms, None),
+            "spmm": dict(roof(local_spmm_bytes, spmm_ms, traffic("spmm")),
                          kernels="spmm_giant_kernel + spmm_heavy_kernel + spmm_light_kernel "
                                  "(three concurrent streams)",
                          gflops=round(2.0 * spmm.local_nnz * FEAT / (spmm_ms * 1e-3) / 1e9, 1),
                          gather_ms=round(float(phase_ms[1]), 4)),
-            "sddmm": dict(roof(local_sddmm_bytes, sddmm_ms, None), kernels="sddmm_tile_kernel",
+            "sddmm": dict(roof(local_sddmm_bytes, sddmm_ms, traffic("sddmm")),
+                          kernels="sddmm_tile_kernel",
                           gflops=round(2.0 * (sddmm.edge_hi - sddmm.edge_lo) * FEAT
                                        / (sddmm_ms * 1e-3) / 1e9, 1),
                           gather_ms=round(float(phase_ms[3]), 4)),

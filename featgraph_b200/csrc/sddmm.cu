@@ -326,13 +326,48 @@ extern "C" int fg_sddmm_coo_f32_host(const int32_t* row, const int32_t* col,
                 cudaGetErrorString(guard.status));
   const size_t sb = sizeof(float) * (size_t)n_cols * feat_len;
   const size_t db = sizeof(float) * (size_t)n_rows * feat_len;
-  const size_t ob = sizeof(float) * (size_t)nnz * num_heads;
   if (sb) FG_CUDA_TRY(cudaMemcpyAsync(src_stage, src_host, sb, cudaMemcpyHostToDevice, st));
   if (db) FG_CUDA_TRY(cudaMemcpyAsync(dst_stage, dst_host, db, cudaMemcpyHostToDevice, st));
-  const int rc = fg_sddmm_coo_f32(row, col, src_stage, dst_stage, out_stage, nnz, n_rows, n_cols,
-                                  feat_len, num_heads, device, stream);
+  // The output (4 bytes per edge and head) dominates the transfers, so the edge list is
+  // cut into pieces: while piece k+1 is computed, piece k travels to the host on a second
+  // stream.  Small inputs take one piece.
+  const int pieces = nnz >= (1 << 22) ? 8 : 1;
+  cudaStream_t copy_st = nullptr;
+  cudaEvent_t done[8] = {nullptr};
+  int rc = FG_OK;
+  cudaError_t err = cudaSuccess;
+  if (pieces > 1) {
+    err = cudaStreamCreateWithFlags(&copy_st, cudaStreamNonBlocking);
+    for (int k = 0; k < pieces && err == cudaSuccess; ++k)
+      err = cudaEventCreateWithFlags(&done[k], cudaEventDisableTiming);
+  }
+  for (int k = 0; k < pieces && rc == FG_OK && err == cudaSuccess; ++k) {
+    const int64_t e0 = nnz * k / pieces, e1 = nnz * (k + 1) / pieces;
+    if (e1 == e0) continue;
+    rc = fg_sddmm_coo_f32(row + e0, col + e0, src_stage, dst_stage, out_stage + e0 * num_heads,
+                          e1 - e0, n_rows, n_cols, feat_len, num_heads, device, stream);
+    if (rc != FG_OK) break;
+    const size_t bytes = sizeof(float) * (size_t)(e1 - e0) * num_heads;
+    if (pieces > 1) {
+      err = cudaEventRecord(done[k], st);
+      if (err == cudaSuccess) err = cudaStreamWaitEvent(copy_st, done[k], 0);
+      if (err == cudaSuccess)
+        err = cudaMemcpyAsync(out_host + e0 * num_heads, out_stage + e0 * num_heads, bytes,
+                              cudaMemcpyDeviceToHost, copy_st);
+    } else {
+      err = cudaMemcpyAsync(out_host + e0 * num_heads, out_stage + e0 * num_heads, bytes,
+                            cudaMemcpyDeviceToHost, st);
+    }
+  }
+  if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+  if (copy_st) {
+    if (err == cudaSuccess) err = cudaStreamSynchronize(copy_st);
+    for (int k = 0; k < pieces; ++k)
+      if (done[k]) cudaEventDestroy(done[k]);
+    cudaStreamDestroy(copy_st);
+  }
   if (rc != FG_OK) return rc;
-  if (ob) FG_CUDA_TRY(cudaMemcpyAsync(out_host, out_stage, ob, cudaMemcpyDeviceToHost, st));
-  FG_CUDA_TRY(cudaStreamSynchronize(st));
+  if (err != cudaSuccess)
+    return fail(FG_ERR_CUDA, "fg_sddmm_coo_f32_host: %s", cudaGetErrorString(err));
   return FG_OK;
 }

@@ -187,6 +187,12 @@ def test_full_size_properties(full):
     ones = torch.ones(g.n_cols, 64, device="cuda")
     out = m.run([ones, ones]).torch
     assert torch.equal(out, torch.full_like(out, 64.0))
+    # the host-buffer entry point cuts a list this long into pieces and overlaps the download
+    ones_host = torch.ones(g.n_cols, 64).pin_memory()
+    out_host = torch.zeros(g.nnz).pin_memory()
+    m.out_tvm.torch.zero_()
+    m.run_host(ones_host, ones_host, out_host)
+    assert torch.equal(out_host, torch.full_like(out_host, 64.0))
     ar = torch.arange(g.n_cols, device="cuda")
     ind = torch.zeros(g.n_cols, 64, device="cuda")
     ind[ar, ar % 64] = 1

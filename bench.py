@@ -230,6 +230,10 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
+        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; the contract of this
+        # script is one JSON line on stdout
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     g, x, y2 = make_inputs(args, device)
@@ -237,8 +241,9 @@ def run_gpu(args):
     rows_dev = g.coo_rows()
     n, nnz = g.n_rows, g.nnz
 
-    spmm = ShardedSpMM(adj, FEAT, device)
-    sddmm = ShardedSDDMM(rows_dev, g.indices, n, g.n_cols, FEAT, device)
+    fused = not args.nccl_gather
+    spmm = ShardedSpMM(adj, FEAT, device, fused_gather=fused)
+    sddmm = ShardedSDDMM(rows_dev, g.indices, n, g.n_cols, FEAT, device, fused_gather=fused)
     stream = torch.cuda.current_stream(device)
 
     def barrier():
@@ -359,7 +364,8 @@ def run_gpu(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name(g), "graph_seed": graphs.GRAPH_SEED,
                        "degree": g.degree_stats(), "parallelism":
-                           "spmm: nnz-balanced row blocks; sddmm: edge ranges; x%d" % world,
+                           "spmm: nnz-balanced row blocks; sddmm: edge ranges; x%d; outputs "
+                           "assembled by %s" % (world, spmm.gather_mode),
                        "l2": "adjacency streams (0.9 GB per kernel) exceed L2 between launches; "
                              "no explicit flush"},
             "e2e": {"value": round(e2e_value, 1), "unit": UNIT,
@@ -468,6 +474,8 @@ def main():
     ap.add_argument("--reference-budget", type=float, default=90.0,
                     help="seconds of CPU work for the whole --impl reference run")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="assemble outputs with NCCL collectives instead of peer stores")
     args = ap.parse_args()
     if args.steps < 1:
         raise SystemExit("--steps must be at least 1")

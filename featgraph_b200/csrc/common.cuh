@@ -13,6 +13,15 @@
 
 namespace fg {
 
+// Where a kernel writes its result: the caller's own buffer and, in a multi-GPU run,
+// the same position in the buffers of up to seven peers (peer-mapped pointers, plain
+// stores over NVLink) -- the "all-gather" then happens inside the kernel's epilogue.
+constexpr int kMaxOutputs = 8;
+struct OutPtrs {
+  float* p[kMaxOutputs];
+  int n;
+};
+
 // ---- host side: per-thread error message -----------------------------------
 std::string& last_error();
 int fail(int code, const char* fmt, ...);

@@ -47,7 +47,7 @@ template <int HEAD_DIM>
 __global__ void __launch_bounds__(kSdWarps * 32)
 sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
                   const float* __restrict__ src, const float* __restrict__ dst,
-                  float* __restrict__ out, long long nnz, int F, int H, int tiles_per_warp) {
+                  OutPtrs out, long long nnz, int F, int H, int tiles_per_warp) {
   constexpr unsigned kFull = 0xffffffffu;
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x & 31;
@@ -162,14 +162,16 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
       acc = mul_then_add(acc, a.z, b.z);
       acc = mul_then_add(acc, a.w, b.w);
       if (HEAD_DIM > 0 && ((q + 1) * 4) % (HEAD_DIM > 0 ? HEAD_DIM : 4) == 0) {
-        if (e < nnz) out[(size_t)e * H + head] = acc;
+        if (e < nnz)
+          for (int o = 0; o < out.n; ++o) out.p[o][(size_t)e * H + head] = acc;
         ++head;
         acc = 0.f;
       }
     }
     ++chunk;
     if (HEAD_DIM == 0 && chunk % chunks_per_head == 0) {
-      if (e < nnz) out[(size_t)e * H + head] = acc;
+      if (e < nnz)
+        for (int o = 0; o < out.n; ++o) out.p[o][(size_t)e * H + head] = acc;
       ++head;
       acc = 0.f;
     }
@@ -189,7 +191,7 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
 __global__ void __launch_bounds__(256)
 sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
                      const float* __restrict__ src, const float* __restrict__ dst,
-                     float* __restrict__ out, long long n_out, int F, int H) {
+                     OutPtrs out, long long n_out, int F, int H) {
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= n_out) return;
   const long long e = i / H;
@@ -199,7 +201,7 @@ sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
   const float* d = dst + (size_t)row[e] * F + (size_t)h * D;
   float acc = 0.f;
   for (int k = 0; k < D; ++k) acc = mul_then_add(acc, s[k], d[k]);
-  out[i] = acc;
+  for (int o = 0; o < out.n; ++o) out.p[o][i] = acc;
 }
 
 constexpr int kSdTilesPerWarp = 16;
@@ -245,11 +247,18 @@ extern "C" int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_head
   return FG_OK;
 }
 
-extern "C" int fg_sddmm_coo_f32(const int32_t* row, const int32_t* col, const float* src,
-                                const float* dst, float* out, int64_t nnz, int64_t n_rows,
-                                int64_t n_cols, int32_t feat_len, int32_t num_heads,
-                                int32_t device, void* stream) {
+extern "C" int fg_sddmm_coo_f32_multi(const int32_t* row, const int32_t* col, const float* src,
+                                      const float* dst, float* const* outs, int32_t n_outs,
+                                      int64_t nnz, int64_t n_rows, int64_t n_cols,
+                                      int32_t feat_len, int32_t num_heads, int32_t device,
+                                      void* stream) {
   using namespace fg;
+  if (!outs || n_outs < 1 || n_outs > kMaxOutputs)
+    return fail(FG_ERR_INVALID_ARGUMENT, "need 1 to %d output pointers, got %d", kMaxOutputs,
+                (int)n_outs);
+  OutPtrs out;
+  out.n = n_outs;
+  for (int q = 0; q < kMaxOutputs; ++q) out.p[q] = q < n_outs ? outs[q] : nullptr;
   if (nnz < 0 || n_rows < 0 || n_cols < 0 || feat_len <= 0 || num_heads <= 0)
     return fail(FG_ERR_INVALID_ARGUMENT, "bad shape: nnz=%lld n_rows=%lld n_cols=%lld feat_len=%d heads=%d",
                 (long long)nnz, (long long)n_rows, (long long)n_cols, (int)feat_len, (int)num_heads);
@@ -259,8 +268,9 @@ extern "C" int fg_sddmm_coo_f32(const int32_t* row, const int32_t* col, const fl
   if (n_rows >= INT32_MAX || n_cols >= INT32_MAX)
     return fail(FG_ERR_UNSUPPORTED, "row/column counts must fit int32");
   if (nnz == 0) return FG_OK;
-  if (!row || !col || !src || !dst || !out)
-    return fail(FG_ERR_INVALID_ARGUMENT, "null device pointer");
+  if (!row || !col || !src || !dst) return fail(FG_ERR_INVALID_ARGUMENT, "null device pointer");
+  for (int q = 0; q < n_outs; ++q)
+    if (!outs[q]) return fail(FG_ERR_INVALID_ARGUMENT, "output pointer %d is null", q);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   DeviceGuard guard(device);
   if (guard.status != cudaSuccess)
@@ -306,6 +316,16 @@ extern "C" int fg_sddmm_coo_f32(const int32_t* row, const int32_t* col, const fl
 #undef FG_SD_LAUNCH
   FG_CUDA_TRY(cudaGetLastError());
   return FG_OK;
+}
+
+extern "C" int fg_sddmm_coo_f32(const int32_t* row, const int32_t* col, const float* src,
+                                const float* dst, float* out, int64_t nnz, int64_t n_rows,
+                                int64_t n_cols, int32_t feat_len, int32_t num_heads,
+                                int32_t device, void* stream) {
+  if (nnz > 0 && !out) return fg::fail(FG_ERR_INVALID_ARGUMENT, "null device pointer");
+  float* outs[1] = {out};
+  return fg_sddmm_coo_f32_multi(row, col, src, dst, nnz > 0 ? outs : outs, 1, nnz, n_rows, n_cols,
+                                feat_len, num_heads, device, stream);
 }
 
 extern "C" int fg_sddmm_coo_f32_host(const int32_t* row, const int32_t* col,

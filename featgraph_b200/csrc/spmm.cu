@@ -40,7 +40,7 @@ template <int G>
 __global__ void __launch_bounds__(256)
 spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
-                  float* __restrict__ Y, const int* __restrict__ rows, int n_listed,
+                  OutPtrs Y, const int* __restrict__ rows, int n_listed,
                   long long n_items, int F) {
   constexpr unsigned kFull = 0xffffffffu;
   const int gl = threadIdx.x % G;  // lane within the group
@@ -113,7 +113,9 @@ spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     if (cnt > 0) e += (cnt < G ? cnt : G);
   }
   if (valid)
-    st_stream4(Y + (size_t)row * F + col_off, make_float4(acc_lo.x, acc_lo.y, acc_hi.x, acc_hi.y));
+    for (int q = 0; q < Y.n; ++q)
+      st_stream4(Y.p[q] + (size_t)row * F + col_off,
+                 make_float4(acc_lo.x, acc_lo.y, acc_hi.x, acc_hi.y));
 }
 
 constexpr int kHvEdges = 32;    // nonzeros per stage
@@ -162,11 +164,15 @@ __device__ __forceinline__ void heavy_consume_stage(const float (*xt)[32 * VEC],
 }
 
 template <int VEC>
-__device__ __forceinline__ void heavy_store_row(float* yslab, int lane, float acc_a, float acc_b) {
-  if (VEC == 2)
-    __stcs(reinterpret_cast<float2*>(yslab + lane * 2), make_float2(acc_a, acc_b));
-  else
-    __stcs(yslab + lane, acc_a);
+__device__ __forceinline__ void heavy_store_row(const OutPtrs& Y, size_t slab_off, int lane,
+                                                float acc_a, float acc_b) {
+  for (int q = 0; q < Y.n; ++q) {
+    float* yslab = Y.p[q] + slab_off;
+    if (VEC == 2)
+      __stcs(reinterpret_cast<float2*>(yslab + lane * 2), make_float2(acc_a, acc_b));
+    else
+      __stcs(yslab + lane, acc_a);
+  }
 }
 
 // Decodes blockIdx.x of the heavy / giant kernels: items are ordered
@@ -187,7 +193,7 @@ template <int VEC>
 __global__ void __launch_bounds__(32)
 spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
-                  float* __restrict__ Y, const int* __restrict__ rows, int n_listed,
+                  OutPtrs Y, const int* __restrict__ rows, int n_listed,
                   int subs_per_slab, int F) {
   constexpr int kSlab = 32 * VEC;                 // floats per gathered segment
   constexpr int kLanesPerRow = kSlab / 4;         // 16-byte copies per segment
@@ -265,7 +271,7 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
                              min(kHvEdges, deg - i * kHvEdges), lane, acc_a, acc_b);
   }
   cp_async_wait<0>();
-  heavy_store_row<VEC>(Y + (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
+  heavy_store_row<VEC>(Y, (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
 }
 
 constexpr int kGtWarps = 12;      // warps per CTA; warp 0 consumes, warps 4 and 8 retire
@@ -305,7 +311,7 @@ template <int VEC>
 __global__ void __launch_bounds__(32 * kGtWarps)
 spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
-                  float* __restrict__ Y, const int* __restrict__ rows, int n_listed,
+                  OutPtrs Y, const int* __restrict__ rows, int n_listed,
                   int subs_per_slab, int F, int* __restrict__ status) {
   constexpr unsigned kFull = 0xffffffffu;
   constexpr int kSlab = 32 * VEC;
@@ -477,14 +483,14 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     if (lane == 0) atomicExch(status, kGtErrConsumerTimeout);
     return;  // the row is not written; the host sees the status
   }
-  heavy_store_row<VEC>(Y + (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
+  heavy_store_row<VEC>(Y, (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
 }
 
 // Fallback for any feat_len / alignment: one warp per row, lanes over features.
 __global__ void __launch_bounds__(256)
 spmm_generic_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                     const float* __restrict__ vals, const float* __restrict__ X,
-                    float* __restrict__ Y, long long n_rows, int F) {
+                    OutPtrs Y, long long n_rows, int F) {
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= n_rows) return;
@@ -495,7 +501,7 @@ spmm_generic_kernel(const int* __restrict__ indptr, const int* __restrict__ indi
     if (f < F) {
       for (int e = beg; e < end; ++e)
         acc = mul_then_add(acc, vals[e], X[(size_t)indices[e] * F + f]);
-      Y[(size_t)row * F + f] = acc;
+      for (int q = 0; q < Y.n; ++q) Y.p[q][(size_t)row * F + f] = acc;
     }
   }
 }
@@ -738,7 +744,7 @@ namespace fg {
 
 template <int G>
 static void launch_light(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
-                         const float* vals, const float* x, float* y, cudaStream_t st) {
+                         const float* vals, const float* x, const OutPtrs& y, cudaStream_t st) {
   const long long items = (long long)p->n_light * (p->feat_len / (4 * G));
   const long long grid = (items + 256 / G - 1) / (256 / G);
   spmm_light_kernel<G><<<(unsigned)grid, 256, 0, st>>>(
@@ -748,13 +754,24 @@ static void launch_light(const fg_spmm_plan* p, const int32_t* indptr, const int
 
 }  // namespace fg
 
-extern "C" int fg_spmm_csr_f32(const fg_spmm_plan* p, const int32_t* indptr,
-                               const int32_t* indices, const float* vals, const float* x,
-                               float* y, void* stream) {
+extern "C" int fg_spmm_csr_f32_multi(const fg_spmm_plan* p, const int32_t* indptr,
+                                     const int32_t* indices, const float* vals, const float* x,
+                                     float* const* ys, int32_t n_ys, void* stream) {
   using namespace fg;
   if (!p) return fail(FG_ERR_INVALID_ARGUMENT, "plan is null");
+  if (!ys || n_ys < 1 || n_ys > kMaxOutputs)
+    return fail(FG_ERR_INVALID_ARGUMENT, "need 1 to %d output pointers, got %d", kMaxOutputs,
+                (int)n_ys);
   if (p->n_rows == 0) return FG_OK;
-  if (!indptr || !y) return fail(FG_ERR_INVALID_ARGUMENT, "indptr_dev or y_dev is null");
+  OutPtrs y;
+  y.n = n_ys;
+  bool aligned = reinterpret_cast<uintptr_t>(x) % 16 == 0;
+  for (int q = 0; q < kMaxOutputs; ++q) {
+    y.p[q] = q < n_ys ? ys[q] : nullptr;
+    if (q < n_ys && !ys[q]) return fail(FG_ERR_INVALID_ARGUMENT, "output pointer %d is null", q);
+    if (q < n_ys && reinterpret_cast<uintptr_t>(ys[q]) % 16 != 0) aligned = false;
+  }
+  if (!indptr) return fail(FG_ERR_INVALID_ARGUMENT, "indptr_dev is null");
   if (p->nnz > 0 && (!indices || !vals || !x))
     return fail(FG_ERR_INVALID_ARGUMENT, "indices_dev, vals_dev or x_dev is null");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -763,8 +780,6 @@ extern "C" int fg_spmm_csr_f32(const fg_spmm_plan* p, const int32_t* indptr,
     return fail(FG_ERR_CUDA, "cannot select device %d: %s", p->device,
                 cudaGetErrorString(guard.status));
 
-  const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
-                       (reinterpret_cast<uintptr_t>(y) % 16 == 0);
   if (!p->vector_ok || !aligned) {
     const long long grid = (p->n_rows + 7) / 8;
     spmm_generic_kernel<<<(unsigned)grid, 256, 0, st>>>(indptr, indices, vals, x, y, p->n_rows,
@@ -820,6 +835,15 @@ extern "C" int fg_spmm_csr_f32(const fg_spmm_plan* p, const int32_t* indptr,
   if (p->n_giant > 0) FG_CUDA_TRY(cudaStreamWaitEvent(st, p->join_giant, 0));
   if (p->n_heavy > 0) FG_CUDA_TRY(cudaStreamWaitEvent(st, p->join_heavy, 0));
   return FG_OK;
+}
+
+extern "C" int fg_spmm_csr_f32(const fg_spmm_plan* p, const int32_t* indptr,
+                               const int32_t* indices, const float* vals, const float* x,
+                               float* y, void* stream) {
+  if (p && p->n_rows > 0 && !y)
+    return fg::fail(FG_ERR_INVALID_ARGUMENT, "indptr_dev or y_dev is null");
+  float* ys[1] = {y};
+  return fg_spmm_csr_f32_multi(p, indptr, indices, vals, x, ys, 1, stream);
 }
 
 extern "C" int fg_spmm_csr_f32_host(const fg_spmm_plan* p, const int32_t* indptr,

@@ -37,6 +37,27 @@ def shard_edges(nnz, world):
     return np.array(bounds[:], dtype=np.int64)
 
 
+def _symmetric_buffer(numel, device, group, world):
+    """A float32 buffer of ``numel`` elements that every rank of the group can address
+    directly (torch symmetric memory over NVLink), or None if that cannot be set up on
+    every rank.  Returns (tensor, handle)."""
+    ok, buf, hdl = 1, None, None
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+        pg = group if group is not None else dist.group.WORLD
+        buf = symm_mem.empty(max(int(numel), 1), dtype=torch.float32, device=device)
+        hdl = symm_mem.rendezvous(buf, pg)
+        if len(hdl.buffer_ptrs) != world:
+            ok = 0
+    except Exception:                      # no peer access / API missing: use NCCL instead
+        ok = 0
+    flag = torch.tensor([ok], device=device, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    if int(flag) == 0:
+        return None, None
+    return buf, hdl
+
+
 def _group_info(group):
     if group is None and not dist.is_initialized():
         return 0, 1
@@ -51,10 +72,12 @@ class ShardedSpMM(object):
     device        : torch device of this rank
     """
 
-    def __init__(self, adj_scipy_csr, feat_len, device, group=None, schedule_args=None):
+    def __init__(self, adj_scipy_csr, feat_len, device, group=None, schedule_args=None,
+                 fused_gather=True):
         self.group = group
         self.rank, self.world = _group_info(group)
         self.device = torch.device(device)
+        self._symm = None
         self.n_rows, self.n_cols = adj_scipy_csr.shape
         self.feat_len = int(feat_len)
         self.bounds = shard_rows_by_nnz(adj_scipy_csr.indptr, self.world)
@@ -66,11 +89,26 @@ class ShardedSpMM(object):
                                (ptr[lo:hi + 1] - ptr[lo]).astype(ptr.dtype)),
                               shape=(hi - lo, self.n_cols))
         self.local_nnz = e1 - e0
-        self.out = torch.zeros(self.n_rows, self.feat_len, dtype=torch.float32,
-                               device=self.device)
+        self.out = None
+        if fused_gather and self.world > 1 and self.device.type == "cuda":
+            # the kernels store every finished row into all peers' outputs themselves
+            buf, hdl = _symmetric_buffer(self.n_rows * self.feat_len, self.device, group,
+                                         self.world)
+            if buf is not None:
+                self.out = buf[:self.n_rows * self.feat_len].view(self.n_rows, self.feat_len)
+                self.out.zero_()
+                self._symm = hdl
+        if self.out is None:
+            self.out = torch.zeros(self.n_rows, self.feat_len, dtype=torch.float32,
+                                   device=self.device)
         self._views = [self.out[int(self.bounds[k]):int(self.bounds[k + 1])]
                        for k in range(self.world)]
         self._local = self.make_local(local, dict(schedule_args or {}))
+        if self._symm is not None:
+            off = self.row_lo * self.feat_len * 4
+            self.module.set_extra_outputs([int(p) + off for r, p in
+                                           enumerate(self._symm.buffer_ptrs) if r != self.rank])
+            self._symm.barrier()
 
     def make_local(self, local_csr, schedule_args):
         """Build the rank-local operator: ``f(x) -> None`` writing rows [row_lo, row_hi)."""
@@ -81,12 +119,21 @@ class ShardedSpMM(object):
         self.module = m
         return lambda x: m.run([x])
 
+    @property
+    def gather_mode(self):
+        """'peer_stores' (kernels write into every rank's output), 'nccl', or 'none'."""
+        return "none" if self.world == 1 else ("peer_stores" if self._symm is not None else "nccl")
+
     def compute_local(self, x):
         self._local(x)
 
     def gather(self):
-        """Uneven all-gather of the row blocks: one broadcast per owner."""
+        """Uneven all-gather of the row blocks: one broadcast per owner -- or, with the
+        fused path, just the barrier after which every rank's stores have landed."""
         if self.world == 1:
+            return
+        if self._symm is not None:
+            self._symm.barrier()
             return
         for k in range(self.world):
             if self._views[k].numel():
@@ -125,10 +172,12 @@ class ShardedSDDMM(object):
     row, col : the FULL edge list (numpy int32 or torch tensors); every rank passes the same
     """
 
-    def __init__(self, row, col, n_rows, n_cols, feat_shape, device, group=None):
+    def __init__(self, row, col, n_rows, n_cols, feat_shape, device, group=None,
+                 fused_gather=True):
         self.group = group
         self.rank, self.world = _group_info(group)
         self.device = torch.device(device)
+        self._symm = None
         self.n_rows, self.n_cols = int(n_rows), int(n_cols)
         self.feat_shape = (feat_shape,) if isinstance(feat_shape, int) else tuple(feat_shape)
         self.num_heads = self.feat_shape[0] if len(self.feat_shape) == 2 else 1
@@ -138,13 +187,27 @@ class ShardedSDDMM(object):
         lo = min(self.rank * self.chunk, self.nnz)
         hi = min(lo + self.chunk, self.nnz)
         self.edge_lo, self.edge_hi = lo, hi
-        self._padded = torch.zeros(self.world * self.chunk * self.num_heads,
-                                   dtype=torch.float32, device=self.device)
+        self._padded = None
+        if fused_gather and self.world > 1 and self.device.type == "cuda":
+            buf, hdl = _symmetric_buffer(self.world * self.chunk * self.num_heads, self.device,
+                                         group, self.world)
+            if buf is not None:
+                self._padded = buf[:self.world * self.chunk * self.num_heads]
+                self._padded.zero_()
+                self._symm = hdl
+        if self._padded is None:
+            self._padded = torch.zeros(self.world * self.chunk * self.num_heads,
+                                       dtype=torch.float32, device=self.device)
         out_shape = (self.nnz, self.num_heads) if len(self.feat_shape) == 2 else (self.nnz,)
         self.out = self._padded[:self.nnz * self.num_heads].view(out_shape)
         self._slot = self._padded[self.rank * self.chunk * self.num_heads:
                                   (self.rank + 1) * self.chunk * self.num_heads]
         self._local = self.make_local(row[lo:hi], col[lo:hi])
+        if self._symm is not None:
+            off = self.rank * self.chunk * self.num_heads * 4
+            self.module.set_extra_outputs([int(p) + off for r, p in
+                                           enumerate(self._symm.buffer_ptrs) if r != self.rank])
+            self._symm.barrier()
 
     def make_local(self, row_local, col_local):
         from .module import VanillaSDDMMcuda
@@ -162,13 +225,20 @@ class ShardedSDDMM(object):
         self.module = m
         return lambda src, dst: m.run([src, dst])
 
+    @property
+    def gather_mode(self):
+        return "none" if self.world == 1 else ("peer_stores" if self._symm is not None else "nccl")
+
     def compute_local(self, src, dst):
         if self.edge_hi > self.edge_lo:
             self._local(src, dst)
 
     def gather(self):
         if self.world > 1 and self.chunk:
-            dist.all_gather_into_tensor(self._padded, self._slot, group=self.group)
+            if self._symm is not None:
+                self._symm.barrier()      # every rank's stores into this buffer have landed
+            else:
+                dist.all_gather_into_tensor(self._padded, self._slot, group=self.group)
 
     def run(self, src, dst):
         """src (n_cols, ...) is indexed by col, dst (n_rows, ...) by row, both replicated.

@@ -105,8 +105,23 @@ class SDDMMbase(object):
                                                  out.attrs["num_heads"], buf, len(buf)))
         return buf.value.decode() + " | hints: %r" % (sched.hints,)
 
+    def set_extra_outputs(self, device_pointers):
+        """Also store every result at these device addresses (peer-mapped copies of this
+        edge range's output on other GPUs, at most 7): the multi-GPU path's fused all-gather."""
+        self._extra_outputs = [int(p) for p in device_pointers]
+
     def _launch(self, src, dst):
         a = self._spec.attrs
+        extra = getattr(self, "_extra_outputs", None)
+        if extra:
+            import ctypes
+            outs = (ctypes.c_void_p * (1 + len(extra)))(self.out_tvm.torch.data_ptr(), *extra)
+            _lib.check(_lib.load().fg_sddmm_coo_f32_multi(
+                ptr(self._adj_row_indices_tvm.torch), ptr(self._adj_col_indices_tvm.torch),
+                ptr(src), ptr(dst), outs, len(outs), self._adj_row_indices.shape[0],
+                self._num_rows, self._num_cols, a["feat_len"], a["num_heads"],
+                self._ctx.device_id, current_stream_handle(self._ctx)))
+            return
         _lib.check(_lib.load().fg_sddmm_coo_f32(
             ptr(self._adj_row_indices_tvm.torch), ptr(self._adj_col_indices_tvm.torch),
             ptr(src), ptr(dst), ptr(self.out_tvm.torch), self._adj_row_indices.shape[0],

@@ -132,7 +132,20 @@ class SpMMbase(object):
         return buf.value.decode() + " | hints: %r" % (sched.hints,)
 
     # -- run -----------------------------------------------------------------------------
+    def set_extra_outputs(self, device_pointers):
+        """Also store every result row at these device addresses (peer-mapped copies of the
+        output block on other GPUs, at most 7): the multi-GPU path's fused all-gather."""
+        self._extra_outputs = [int(p) for p in device_pointers]
+
     def _launch(self, x):
+        extra = getattr(self, "_extra_outputs", None)
+        if extra:
+            outs = (ctypes.c_void_p * (1 + len(extra)))(self.out_tvm.torch.data_ptr(), *extra)
+            _lib.check(_lib.load().fg_spmm_csr_f32_multi(
+                self._plan, ptr(self._adj_indptr_tvm.torch), ptr(self._adj_indices_tvm.torch),
+                ptr(self._adj_vals_tvm.torch), ptr(x), outs, len(outs),
+                current_stream_handle(self._ctx)))
+            return
         _lib.check(_lib.load().fg_spmm_csr_f32(
             self._plan, ptr(self._adj_indptr_tvm.torch), ptr(self._adj_indices_tvm.torch),
             ptr(self._adj_vals_tvm.torch), ptr(x), ptr(self.out_tvm.torch),

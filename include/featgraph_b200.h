@@ -79,6 +79,18 @@ int fg_spmm_csr_f32(const fg_spmm_plan* plan, const int32_t* indptr_dev,
                     const int32_t* indices_dev, const float* vals_dev,
                     const float* x_dev, float* y_dev, void* stream);
 
+/* The same SpMM with its result written to n_ys buffers at once (1 <= n_ys <= 8):
+ * ys_host_array[0] is normally the caller's own Y block, the others the same block
+ * inside the Y of peer GPUs (peer-mapped device pointers).  The kernels store every
+ * finished row to all of them (plain stores over NVLink), so on a multi-GPU run the
+ * all-gather of the row blocks happens in the kernels' epilogue; the caller still
+ * has to synchronise the GPUs before the peers read.  No counterpart in the
+ * reference (single device, python/featgraph/module/spmm.py:218). */
+int fg_spmm_csr_f32_multi(const fg_spmm_plan* plan, const int32_t* indptr_dev,
+                          const int32_t* indices_dev, const float* vals_dev,
+                          const float* x_dev, float* const* ys_host_array, int32_t n_ys,
+                          void* stream);
+
 /* Same computation from HOST buffers: uploads X, launches, downloads Y and
  * synchronises the stream.  The adjacency stays resident on the device, as it
  * does in the reference after SpMMbase.__init__
@@ -130,6 +142,15 @@ int fg_sddmm_coo_f32(const int32_t* row_dev, const int32_t* col_dev,
                      int64_t nnz, int64_t n_rows, int64_t n_cols,
                      int32_t feat_len, int32_t num_heads, int32_t device,
                      void* stream);
+
+/* The same SDDMM with its result written to n_outs buffers at once (see
+ * fg_spmm_csr_f32_multi): outs_host_array[i] points at the position of this call's
+ * first edge inside output buffer i.  No counterpart in the reference. */
+int fg_sddmm_coo_f32_multi(const int32_t* row_dev, const int32_t* col_dev,
+                           const float* src_dev, const float* dst_dev,
+                           float* const* outs_host_array, int32_t n_outs, int64_t nnz,
+                           int64_t n_rows, int64_t n_cols, int32_t feat_len,
+                           int32_t num_heads, int32_t device, void* stream);
 
 /* Same computation from HOST feature buffers (edge lists stay resident, as in
  * SDDMMbase.__init__, python/featgraph/module/sddmm.py:59-60). */

@@ -42,25 +42,35 @@ def _worker(rank, world, port):
         dist.all_gather(gathered, probe)
         assert all(torch.equal(t, probe) for t in gathered)
 
-        spmm = ShardedSpMM(adj, 64, dev)
-        y = spmm.run(x)
-        torch.cuda.synchronize(dev)
-        want = fg_oracle.spmm_csr_f32(adj.indptr, adj.indices, adj.data, x.cpu().numpy())
-        assert np.array_equal(bits(want), bits(y.cpu().numpy())), "rank %d SpMM" % rank
-        assert spmm.module.device_status() == 0
-        per_rank = np.diff(adj.indptr[spmm.bounds])
-        assert per_rank.max() - per_rank.min() <= np.diff(adj.indptr).max()
-
+        want_y = fg_oracle.spmm_csr_f32(adj.indptr, adj.indices, adj.data, x.cpu().numpy())
         rows = g.coo_rows()
-        for shape, heads in (((64,), 1), ((4, 16), 4)):
-            sd = ShardedSDDMM(rows, g.indices, g.n_rows, g.n_cols, shape, dev)
-            out = sd.run(y2.view((-1,) + shape), x.view((-1,) + shape))
+        modes = set()
+        # fused: kernels store into every peer's output (symmetric memory); else NCCL gathers
+        for fused in (True, False):
+            spmm = ShardedSpMM(adj, 64, dev, fused_gather=fused)
+            modes.add(spmm.gather_mode)
+            for _ in range(2):                   # the second call overwrites the first's result
+                y = spmm.run(x)
             torch.cuda.synchronize(dev)
-            want = fg_oracle.sddmm_coo_f32(rows.cpu().numpy(), g.indices.cpu().numpy(),
-                                           y2.cpu().numpy(), x.cpu().numpy(), num_heads=heads,
-                                           parallel=True)
-            assert np.array_equal(bits(want.reshape(out.shape)), bits(out.cpu().numpy())), \
-                "rank %d SDDMM %r" % (rank, shape)
+            dist.barrier()
+            assert np.array_equal(bits(want_y), bits(y.cpu().numpy())), \
+                "rank %d SpMM (%s)" % (rank, spmm.gather_mode)
+            assert spmm.module.device_status() == 0
+            per_rank = np.diff(adj.indptr[spmm.bounds])
+            assert per_rank.max() - per_rank.min() <= np.diff(adj.indptr).max()
+            for shape, heads in (((64,), 1), ((4, 16), 4)):
+                sd = ShardedSDDMM(rows, g.indices, g.n_rows, g.n_cols, shape, dev,
+                                  fused_gather=fused)
+                out = sd.run(y2.view((-1,) + shape), x.view((-1,) + shape))
+                torch.cuda.synchronize(dev)
+                dist.barrier()
+                want = fg_oracle.sddmm_coo_f32(rows.cpu().numpy(), g.indices.cpu().numpy(),
+                                               y2.cpu().numpy(), x.cpu().numpy(),
+                                               num_heads=heads, parallel=True)
+                assert np.array_equal(bits(want.reshape(out.shape)), bits(out.cpu().numpy())), \
+                    "rank %d SDDMM %r (%s)" % (rank, shape, sd.gather_mode)
+            del spmm, sd
+        assert "nccl" in modes
     finally:
         dist.destroy_process_group()
 

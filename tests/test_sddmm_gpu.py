@@ -219,3 +219,21 @@ def test_full_size_sampled_edges_against_oracle(full, oracle, heads, dim):
     want = oracle.sddmm_coo_f32(r, c, src.cpu().numpy(), dst.cpu().numpy(), num_heads=heads,
                                 parallel=True)
     assert np.array_equal(bits(want), bits(out1[sel].cpu().numpy()))
+
+
+@pytest.mark.parametrize("shape", [(64,), (4, 16), (100,)])
+def test_extra_outputs_receive_the_same_results(oracle, shape):
+    # fg_sddmm_coo_f32_multi: tile kernel (64; 4 x 16) and generic kernel (100)
+    coo = random_csr(170, 140, 0.1, seed=31).tocoo()
+    src, dst = features((140,) + shape, seed=32), features((170,) + shape, seed=33)
+    m = VanillaSDDMMcuda(coo)
+    m.build([te.placeholder(src.shape), te.placeholder(dst.shape)], {}, {"num_cuda_blocks": 64})
+    heads = shape[0] if len(shape) == 2 else 1
+    extra = [torch.full((coo.nnz * heads,), float("nan"), device="cuda") for _ in range(3)]
+    m.set_extra_outputs([e.data_ptr() for e in extra])
+    out = m.run([nd.array(src, m.ctx), nd.array(dst, m.ctx)]).asnumpy()
+    torch.cuda.synchronize()
+    want = bits(oracle.sddmm_coo_f32(coo.row, coo.col, src, dst, num_heads=heads))
+    assert np.array_equal(want.reshape(-1), bits(out).reshape(-1))
+    for e in extra:
+        assert np.array_equal(want.reshape(-1), bits(e.cpu().numpy()))

@@ -257,3 +257,27 @@ def test_full_size_sampled_rows_against_oracle(full_graph, full_module, oracle):
     got = y1[torch.from_numpy(picks).cuda()].cpu().numpy()
     assert m.device_status() == 0
     assert np.array_equal(bits(want), bits(got))
+
+
+@pytest.mark.parametrize("threshold", [0, 8])
+def test_extra_outputs_receive_the_same_rows(oracle, threshold):
+    # fg_spmm_csr_f32_multi: every row is stored to each listed buffer (in a multi-GPU run
+    # the extra ones are peers' memory); here two more local buffers stand in for them
+    adj = random_csr(300, 200, 0.08, seed=21)
+    dense = np.zeros(200, bool)
+    dense[::3] = True                                   # a few rows of every class
+    adj = sp.vstack([adj, sp.csr_matrix(np.tile(dense, (2, 1)).astype(np.float32))]).tocsr()
+    x = features((200, 96), seed=22)
+    m = VanillaSpMMcuda(adj)
+    m.build([te.placeholder(x.shape)], {}, {"heavy_row_threshold": threshold})
+    extra = [torch.full((adj.shape[0], 96), float("nan"), device="cuda") for _ in range(2)]
+    m.set_extra_outputs([e.data_ptr() for e in extra])
+    y = m.run([nd.array(x, m.ctx)]).asnumpy()
+    torch.cuda.synchronize()
+    want = bits(oracle_spmm(oracle, adj, x))
+    assert np.array_equal(want, bits(y))
+    for e in extra:
+        assert np.array_equal(want, bits(e.cpu().numpy()))
+    with pytest.raises(_lib.FeatGraphError):
+        m.set_extra_outputs([extra[0].data_ptr()] * 8)  # 1 + 8 outputs: over the limit
+        m.run([nd.array(x, m.ctx)])

@@ -18,11 +18,12 @@
 //       slab); indices/values and the gathered X segments are staged through
 //       shared memory with cp.async rings, which takes the gather latency off
 //       the sequential add chain.
-//   * giant rows (deg > 32768, at most one CTA per SM) -> spmm_giant_kernel: a
-//       consumer warp adds in order while nine producer warps gather, handing
-//       stages over through mbarriers.  The longest row bounds the whole call
-//       (its sum is one dependent chain) and a single warp cannot keep enough
-//       copies in flight to feed that chain.
+//   * giant rows (the few whose chain would outlast the rest of the call) ->
+//       spmm_giant_kernel: one CTA per (row, 32-float slab); six producer warps
+//       gather, multiply and store transposed products into a shared-memory
+//       ring, one consumer warp only adds, in order, at 6.7 cycles per nonzero
+//       (the dependent fp32 add alone takes 4.2).  The longest row bounds the
+//       whole call -- its sum is one dependent chain.
 //   * anything the vector paths cannot take (feat_len not a multiple of 32,
 //     unaligned pointers) -> spmm_generic_kernel, one warp per row.
 #include <algorithm>
@@ -274,57 +275,63 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   heavy_store_row<VEC>(Y, (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
 }
 
-constexpr int kGtWarps = 12;      // warps per CTA; warp 0 consumes, warps 4 and 8 retire
-constexpr int kGtProducers = 9;   // producer warps per CTA (the warps with id % 4 != 0)
-constexpr int kGtSlots = 16;      // ring of stages (power of two)
-constexpr int kGtQueue = 4;       // stages of column indices a producer holds in registers
-constexpr unsigned kGtMaxPolls = 1u << 20;  // bound of every barrier wait
-// A parity wait tells the current phase from the previous one only.  A producer's
-// consecutive stages are kGtProducers apart; were that more than the ring size it
-// would skip a round of a slot and its wait would pass one phase too early.
-static_assert(kGtProducers <= kGtSlots, "a producer may not skip a round of a slot");
+constexpr int kGtWarps = 8;       // warps per CTA; warp 0 consumes, warp 4 retires
+constexpr int kGtProducers = 6;   // producer warps per CTA (warps 1, 2, 3, 5, 6, 7)
+constexpr int kGtGroup = 8;       // 32-nonzero blocks per group: one barrier hand-over per group
+constexpr int kGtGroups = 4;      // ring of groups (power of two)
+constexpr int kGtRing = kGtGroup * kGtGroups;  // blocks in the ring
+constexpr unsigned kGtMaxPolls = 1u << 20;     // bound of a spinning barrier wait (tests)
+// A parity wait can only tell a barrier's current phase from the previous one, so
+// every warp has to look at every phase of every barrier it waits on.  A
+// producer's consecutive blocks are kGtProducers apart; with no more producers
+// than blocks in a group it enters every group of the row, one after the other.
+static_assert(kGtProducers <= kGtGroup, "a producer may not skip a group");
 constexpr int kGtErrProducerTimeout = 1, kGtErrConsumerTimeout = 2;
+constexpr int kGtSmemBytes = kGtRing * kHvEdges * 32 * 4   // products, [block][feature][nonzero]
+                             + (kGtRing + 4) * 4;          // one flag per ring block, group counter
 
-template <int VEC>
-constexpr int giant_smem_bytes() {
-  return kGtSlots * kHvEdges * 32 * VEC * 4   // gathered X segments
-         + kGtSlots * kHvEdges * 4            // values
-         + 2 * kGtSlots * 8;                  // full / empty barriers
-}
+// Quad position of giant_kernel's product layout.  With it both the producers'
+// 16-byte stores (8 lanes = 8 feature quads, one nonzero quad) and the consumer's
+// 16-byte loads (8 lanes = 8 consecutive features, one nonzero quad) spread over
+// all 32 banks.
+__device__ __forceinline__ int giant_swizzle(int f) { return ((f >> 2) ^ f) & 7; }
 
-// One CTA of 1 consumer + kGtProducers producer warps per (giant row, slab).
-// Warps are dealt to the SM's four schedulers round-robin by id, so warps 4 and
-// 8 -- which would share the consumer's scheduler -- retire at once: the add
-// chain keeps a scheduler's issue slots to itself.
+// One CTA per (giant row, 32-float slab): a consumer warp and six producer warps.
 //
 // The sum of one row is a dependent chain (CSR order, one accumulator per
-// feature), so the longest row bounds the whole SpMM.  A single warp cannot feed
-// that chain: it can keep only a few cp.async copies outstanding (measured: 85
-// cycles per 512-byte copy instruction for a lone warp, i.e. 47 cycles per
-// nonzero at 64 features, while the chain itself needs 4 to 6).  Here producer
-// warp w gathers stages w, w+P, w+2P, ... (column indices through a register
-// queue, 16-byte cp.async copies that signal the stage's "full" mbarrier when
-// they land) and the consumer warp adds the stages in order and hands slots
-// back through "empty" mbarriers.  Every barrier wait is a bounded poll; a wait
-// that gives up records a code in *status and the warp leaves.
-template <int VEC>
+// feature), so the longest row bounds the whole SpMM -- on several GPUs even more
+// so, because the chain does not shrink with the shard -- and everything but the
+// add itself has to stay off that chain.  Measured, in cycles per block of 32
+// nonzeros: a lone warp gathering by cp.async 1500 (it keeps only a few copies
+// outstanding); a consumer that reads segments from shared memory, multiplies and
+// adds 290, and 450 beside busy producer warps; adds of ready products from
+// registers 135 -- the chain bound, 4.2 cycles per add; one mbarrier test by a
+// whole warp 180 (the 32 lanes' accesses to the one barrier word serialise, and
+// the instruction that takes the verdict stalls the warp whatever comes after),
+// by one lane 50.  So: producer w takes blocks w, w+6, w+12, ... of the row; it
+// gathers the X segments straight into registers (16-byte loads, three blocks in
+// flight), multiplies by the values and stores the PRODUCTS into the ring; the
+// consumer keeps the next three blocks in registers (lane = feature) while it
+// adds the current one, the loads alternating with the adds in one basic block.
+// Barriers work on groups of 8 blocks and are touched by lane 0 only: "full"
+// counts the 8 blocks' producers, "empty" is the consumer's hand-back once the
+// group sits in its registers.  Warp 4 retires at once: the consumer shares its
+// scheduler with nobody.  Every wait is a bounded poll; a wait that gives up
+// records a code in *status and the warp leaves.
 __global__ void __launch_bounds__(32 * kGtWarps)
 spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
                   OutPtrs Y, const int* __restrict__ rows, int n_listed,
                   int subs_per_slab, int F, int* __restrict__ status) {
   constexpr unsigned kFull = 0xffffffffu;
-  constexpr int kSlab = 32 * VEC;
-  constexpr int kLanesPerRow = kSlab / 4;
-  constexpr int kRowsPerCopy = 32 / kLanesPerRow;
-  constexpr int kCopies = kHvEdges / kRowsPerCopy;
   extern __shared__ __align__(16) unsigned char giant_smem[];
-  float(*xs)[kHvEdges][kSlab] = reinterpret_cast<float(*)[kHvEdges][kSlab]>(giant_smem);
-  float(*val_s)[kHvEdges] =
-      reinterpret_cast<float(*)[kHvEdges]>(giant_smem + kGtSlots * kHvEdges * kSlab * 4);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(giant_smem + kGtSlots * kHvEdges * kSlab * 4 +
-                                                   kGtSlots * kHvEdges * 4);
-  uint64_t* empty_bar = full_bar + kGtSlots;
+  // prod[block][feature][nonzero]: a feature's 32 products of a block are 8 quads of 4
+  // consecutive nonzeros, stored at quad position q ^ giant_swizzle(feature)
+  float(*prod)[32][kHvEdges] = reinterpret_cast<float(*)[32][kHvEdges]>(giant_smem);
+  // ready[s] = 1 + the number of the block whose products sit in ring block s (written
+  // by its producer); *consumed = groups the consumer has handed back
+  unsigned* ready = reinterpret_cast<unsigned*>(giant_smem + kGtRing * kHvEdges * 32 * 4);
+  unsigned* consumed = ready + kGtRing;
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -332,158 +339,259 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   heavy_decode_item(rows, n_listed, subs_per_slab, row, sub);
   const int beg = __ldg(indptr + row);
   const int deg = __ldg(indptr + row + 1) - beg;
-  const int n_stages = (deg + kHvEdges - 1) / kHvEdges;
+  const int n_blocks = (deg + kHvEdges - 1) / kHvEdges;  // incl. a ragged last one
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kGtSlots; ++i) {
-      mbar_init(&full_bar[i], 32);  // one arrival per lane of the producing warp
-      mbar_init(&empty_bar[i], 1);  // one arrival by the consumer
-    }
-  }
+  if (threadIdx.x <= kGtRing) ready[threadIdx.x] = 0;  // the last one is *consumed
   __syncthreads();
 
-  if (warp > 0 && (warp & 3) == 0) return;  // leave the consumer's scheduler alone
+  if (warp == 4) return;  // leave the consumer's scheduler alone
   if (warp > 0) {
     // ------------------------------------------------------------ producer --
     const int* ind = indices + beg;
     const float* val = vals + beg;
-    const int part = (lane % kLanesPerRow) * 4;
-    const int first = lane / kLanesPerRow;
-    const float* xbase = X + (size_t)sub * kSlab + part;
-    const int s_first = warp - 1 - (warp >> 2);  // producer index 0 .. kGtProducers-1
-    int idxq[kGtQueue];
-#pragma unroll
-    for (int u = 0; u < kGtQueue; ++u) {
-      const long long e = (long long)(s_first + u * kGtProducers) * kHvEdges + lane;
-      idxq[u] = e < deg ? ld_stream(ind + e) : 0;
-    }
-    bool ok = true;
-    for (int s0 = s_first; s0 < n_stages && ok; s0 += kGtQueue * kGtProducers) {
-#pragma unroll
-      for (int u = 0; u < kGtQueue; ++u) {
-        const int s = s0 + u * kGtProducers;
-        if (s < n_stages && ok) {
-          const int slot = s & (kGtSlots - 1);
-          const unsigned round = (unsigned)(s / kGtSlots);
-          // slot handed back by the consumer?  (passes at once in round 0)
-          ok = mbar_wait_park(&empty_bar[slot], (round & 1u) ^ 1u, kGtMaxPolls);
-          if (ok) {
-            const int cnt = min(kHvEdges, deg - s * kHvEdges);
-            const int my_idx = idxq[u];
-            const long long e_ahead =
-                (long long)(s + kGtQueue * kGtProducers) * kHvEdges + lane;
-            idxq[u] = e_ahead < deg ? ld_stream(ind + e_ahead) : 0;
-            if (lane < cnt) cp_async4(&val_s[slot][lane], val + s * kHvEdges + lane);
-#pragma unroll
-            for (int k = 0; k < kCopies; ++k) {
-              const int e = first + kRowsPerCopy * k;
-              const int c = __shfl_sync(kFull, my_idx, e);
-              if (e < cnt) cp_async16_cg(&xs[slot][e][part], xbase + (size_t)c * F);
-            }
-            cp_async_arrive_on(&full_bar[slot]);
-          }
-        }
+    const int pw = warp - 1 - (warp >> 2);  // producer index 0 .. kGtProducers-1
+    const int m = lane & 7;                 // this lane's feature quad: 4m .. 4m+3
+    const int g8 = (lane >> 3) * 8;         // and its nonzeros within a block: g8 .. g8+7
+    const float* xbase = X + (size_t)sub * 32 + 4 * m;
+    // the producer's own sequence of blocks u = 0, 1, 2, ...: block pw + u * P of the row
+    int my_blocks = 0;
+    if (pw < n_blocks) my_blocks = (n_blocks - pw + kGtProducers - 1) / kGtProducers;
+    auto load_iv = [&](int u, int& c, float& v) {
+      const long long e = (long long)(pw + u * kGtProducers) * kHvEdges + lane;
+      c = e < deg ? ld_stream(ind + e) : 0;
+      v = e < deg ? ld_stream(val + e) : 0.f;
+    };
+    auto prefetch_iv = [&](int u) {
+      const long long e = (long long)(pw + u * kGtProducers) * kHvEdges + lane;
+      if (e < deg && (lane & 7) == 0) {  // one request per 32-byte sector
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(ind + e));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(val + e));
       }
+    };
+    // this lane's eight columns / values of a block, out of the warp's coalesced copy
+    auto spread = [&](int c, float v, int (&col)[8], float (&vs)[8]) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        col[k] = __shfl_sync(kFull, c, g8 + k);
+        vs[k] = __shfl_sync(kFull, v, g8 + k);
+      }
+    };
+    auto gather = [&](int u, const int (&col)[8], float4 (&x)[8]) {
+      const long long left = (long long)deg - (long long)(pw + u * kGtProducers) * kHvEdges;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        x[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g8 + k < left) x[k] = ld_gather4(xbase + (size_t)col[k] * F);
+      }
+    };
+    bool ok = true;
+    int entered = -1;  // last group whose "empty" barrier this warp has passed
+    auto emit = [&](int u, const float (&vs)[8], const float4 (&x)[8]) {
+      const int b = pw + u * kGtProducers;
+      const int grp = b / kGtGroup;
+      float4 pr[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        pr[k] = make_float4(__fmul_rn(vs[k], x[k].x), __fmul_rn(vs[k], x[k].y),
+                            __fmul_rn(vs[k], x[k].z), __fmul_rn(vs[k], x[k].w));
+      if (grp != entered) {
+        if (grp >= kGtGroups) {  // the ring block has held group grp - kGtGroups: handed back?
+          int got = 0;
+          if (lane == 0) {
+            const unsigned need = (unsigned)(grp - kGtGroups + 1);
+            for (unsigned i = 0; i < kGtMaxPolls && !got; ++i) {
+              got = ld_acquire_shared(consumed) >= need;
+              if (!got) __nanosleep(64);
+            }
+          }
+          __syncwarp();  // lane 0's acquire covers the warp
+          ok = __shfl_sync(kFull, got, 0) != 0;
+          if (!ok) return;
+        }
+        entered = grp;
+      }
+      // the lane holds an 8-nonzero x 4-feature tile: transposed in registers, it
+      // leaves as 8 quads (one feature, 4 consecutive nonzeros each)
+      float(*pt)[kHvEdges] = prod[b & (kGtRing - 1)];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int q = (g8 >> 2) + h;  // quad of nonzeros g8 + 4h .. g8 + 4h + 3
+        *reinterpret_cast<float4*>(&pt[4 * m + 0][(q ^ giant_swizzle(4 * m + 0)) << 2]) =
+            make_float4(pr[4 * h].x, pr[4 * h + 1].x, pr[4 * h + 2].x, pr[4 * h + 3].x);
+        *reinterpret_cast<float4*>(&pt[4 * m + 1][(q ^ giant_swizzle(4 * m + 1)) << 2]) =
+            make_float4(pr[4 * h].y, pr[4 * h + 1].y, pr[4 * h + 2].y, pr[4 * h + 3].y);
+        *reinterpret_cast<float4*>(&pt[4 * m + 2][(q ^ giant_swizzle(4 * m + 2)) << 2]) =
+            make_float4(pr[4 * h].z, pr[4 * h + 1].z, pr[4 * h + 2].z, pr[4 * h + 3].z);
+        *reinterpret_cast<float4*>(&pt[4 * m + 3][(q ^ giant_swizzle(4 * m + 3)) << 2]) =
+            make_float4(pr[4 * h].w, pr[4 * h + 1].w, pr[4 * h + 2].w, pr[4 * h + 3].w);
+      }
+      __syncwarp();  // every lane's stores are ordered before lane 0's release
+      if (lane == 0) st_release_shared(&ready[b & (kGtRing - 1)], (unsigned)b + 1u);
+    };
+    // Batches of three blocks.  A warp has six scoreboards for all its loads and
+    // shuffles in flight, so a wait for any one result tends to wait for the newest
+    // load as well; the batch is therefore ordered to have nothing slow in flight
+    // when something quick is waited for: (1) all shuffles of the batch (columns and
+    // values per lane), (2) all 24 gathers, the next batch's columns / values (they
+    // stream from DRAM, behind an L2 prefetch eight batches ahead) -- one exposed
+    // latency for the lot -- (3) multiply, pass the barrier, store, three times.
+    float4 xa[8], xb[8], xc[8];
+    float vsa[8], vsb[8], vsc[8];
+    int ca, cb, cc;
+    float va, vb, vc;
+    load_iv(0, ca, va);
+    load_iv(1, cb, vb);
+    load_iv(2, cc, vc);
+    for (int u = 0; u < my_blocks && ok; u += 3) {
+      {
+        int cola[8], colb[8], colc[8];
+        spread(ca, va, cola, vsa);
+        spread(cb, vb, colb, vsb);
+        spread(cc, vc, colc, vsc);
+        gather(u, cola, xa);
+        gather(u + 1, colb, xb);
+        gather(u + 2, colc, xc);
+      }
+      load_iv(u + 3, ca, va);
+      load_iv(u + 4, cb, vb);
+      load_iv(u + 5, cc, vc);
+      prefetch_iv(u + 24);
+      prefetch_iv(u + 25);
+      prefetch_iv(u + 26);
+      emit(u, vsa, xa);
+      if (u + 1 < my_blocks && ok) emit(u + 1, vsb, xb);
+      if (u + 2 < my_blocks && ok) emit(u + 2, vsc, xc);
     }
     if (!ok && lane == 0) atomicExch(status, kGtErrProducerTimeout);
-    cp_async_wait_all();
     return;
   }
 
   // -------------------------------------------------------------- consumer --
-  // Software pipeline over the full stages: while the products of stage i are
-  // being added (the dependent chain), the segments of stage i+1 are read from
-  // shared memory and multiplied into a second register set.  A stage's slot is
-  // handed back as soon as its products sit in registers.
-  float acc_a = 0.f, acc_b = 0.f;
-  float pa[kHvEdges], pb[kHvEdges], qa[kHvEdges], qb[kHvEdges];
+  // lane = feature.  Block j lives in register set j % 4; blocks j+1 .. j+3 are
+  // on their way from shared memory while block j is added.
+  float acc = 0.f;
   const int n_full = deg / kHvEdges;
-  bool ok = true;
-  auto wait_stage = [&](int i) {
-    return mbar_wait_spin(&full_bar[i & (kGtSlots - 1)], (unsigned)(i / kGtSlots) & 1u,
-                          kGtMaxPolls);
+  // Every lane reads the flag itself (a broadcast): a relaxed load long before the
+  // check, so that the check costs a compare; the fence behind a successful check
+  // turns it into an acquire (every lane's loads of the block come after it).  A lane
+  // whose bounded wait gives up only notes it; the warp looks at the notes at the end.
+  auto peek = [&](int j) { return ld_relaxed_shared(&ready[j & (kGtRing - 1)]); };
+  bool gave_up = false;
+  auto await = [&](int j, unsigned seen) {
+    const unsigned want = (unsigned)j + 1u;
+    if (seen != want && !gave_up) {  // rare: the producers are behind (once given up, no more waits)
+      bool got = false;
+      for (unsigned i = 0; i < kGtMaxPolls && !got; ++i) got = peek(j) == want;
+      gave_up |= !got;
+    }
+    fence_acquire_cta();
   };
-  auto release_stage = [&](int i) {
-    __syncwarp();  // every lane has read the slot
-    if (lane == 0) mbar_arrive(&empty_bar[i & (kGtSlots - 1)]);
+  auto release_after = [&](int j) {  // after the reads of block j: its group, if j closes it
+    if (j % kGtGroup == kGtGroup - 1) {
+      __syncwarp();  // every lane's reads are ordered before lane 0's release
+      if (lane == 0) st_release_shared(consumed, (unsigned)(j / kGtGroup) + 1u);
+    }
   };
-#define FG_GIANT_PRODUCTS(i, A, B)                                                        \
-  do {                                                                                    \
-    const float(*xt)[kSlab] = xs[(i) & (kGtSlots - 1)];                                   \
-    const float* vt = val_s[(i) & (kGtSlots - 1)];                                        \
-    _Pragma("unroll") for (int e4 = 0; e4 < kHvEdges; e4 += 4) {                          \
-      const float4 v4 = *reinterpret_cast<const float4*>(vt + e4);                        \
-      const float vv[4] = {v4.x, v4.y, v4.z, v4.w};                                       \
-      _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                     \
-        if (VEC == 2) {                                                                   \
-          const float2 xv = *reinterpret_cast<const float2*>(&xt[e4 + q][lane * 2]);      \
-          A[e4 + q] = __fmul_rn(vv[q], xv.x);                                             \
-          B[e4 + q] = __fmul_rn(vv[q], xv.y);                                             \
-        } else {                                                                          \
-          A[e4 + q] = __fmul_rn(vv[q], xt[e4 + q][lane]);                                 \
-          B[e4 + q] = 0.f;                                                                \
-        }                                                                                 \
-      }                                                                                   \
-    }                                                                                     \
-  } while (0)
-#define FG_GIANT_CHAIN(A, B)                                                              \
-  do {                                                                                    \
-    _Pragma("unroll") for (int e = 0; e < kHvEdges; ++e) {                                \
-      acc_a = __fadd_rn(acc_a, A[e]);                                                     \
-      if (VEC == 2) acc_b = __fadd_rn(acc_b, B[e]);                                       \
-    }                                                                                     \
-  } while (0)
+  const int swz = giant_swizzle(lane);
+  auto fetch = [&](int j, float4 (&s)[8]) {  // prologue only
+    if (j >= n_full) return;
+    const float* src = prod[j & (kGtRing - 1)][lane];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) s[q] = *reinterpret_cast<const float4*>(src + ((q ^ swz) << 2));
+    release_after(j);
+  };
+  // Adds the block in sa and reads block jf into sf.  The reads and the adds sit in ONE
+  // basic block, alternating, so that the loads issue in the gaps of the dependent add
+  // chain instead of ahead of it.
+  auto core = [&](const float4 (&sa)[8], float4 (&sf)[8], int jf) {
+    const float* src = prod[jf & (kGtRing - 1)][lane];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      sf[q] = *reinterpret_cast<const float4*>(src + ((q ^ swz) << 2));
+      acc = __fadd_rn(acc, sa[q].x);
+      acc = __fadd_rn(acc, sa[q].y);
+      acc = __fadd_rn(acc, sa[q].z);
+      acc = __fadd_rn(acc, sa[q].w);
+    }
+  };
+  auto chain = [&](const float4 (&sa)[8]) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      acc = __fadd_rn(acc, sa[q].x);
+      acc = __fadd_rn(acc, sa[q].y);
+      acc = __fadd_rn(acc, sa[q].z);
+      acc = __fadd_rn(acc, sa[q].w);
+    }
+  };
+  // One block with its own flag check: the row's tail.
+  unsigned seen = 0;  // flag of the block the next step reads, as of one step ago
+  auto step = [&](int jc, const float4 (&sa)[8], float4 (&sf)[8]) {
+    if (jc >= n_full) return;
+    const int jf = jc + 3;
+    if (jf < n_full) {
+      await(jf, seen);
+      core(sa, sf, jf);
+      seen = peek(jf + 1);
+      release_after(jf);
+    } else {
+      chain(sa);
+    }
+  };
 
-  // products(i+1) and chain(i) share one basic block so that the compiler
-  // interleaves the shared-memory reads and multiplies with the add chain.
-  if (n_full > 0) {
-    ok = wait_stage(0);
-    if (ok) {
-      FG_GIANT_PRODUCTS(0, pa, pb);
-      release_stage(0);
+  float4 s0[8], s1[8], s2[8], s3[8];
+  for (int i = 0; i < kGtGroup && i < n_full; ++i) await(i, 0u);  // group 0, block by block
+  fetch(0, s0);
+  fetch(1, s1);
+  fetch(2, s2);
+  // Whole groups: block j (a multiple of 8) .. j+2 sit in s0 .. s2 and group j/8 has been
+  // checked.  Eight steps add blocks j .. j+7 and read blocks j+3 .. j+10; the flags
+  // of the next group are read in steps 0-3 and checked, all at once, before step 5
+  // reads its first block; the group is handed back after step 4 has read its last.
+  int j = 0;
+  for (; j + 2 * kGtGroup <= n_full; j += kGtGroup) {
+    const int nx = j + kGtGroup;
+    const unsigned f0 = peek(nx), f1 = peek(nx + 1);
+    core(s0, s3, j + 3);
+    const unsigned f2 = peek(nx + 2), f3 = peek(nx + 3);
+    core(s1, s0, j + 4);
+    const unsigned f4 = peek(nx + 4), f5 = peek(nx + 5);
+    core(s2, s1, j + 5);
+    const unsigned f6 = peek(nx + 6), f7 = peek(nx + 7);
+    core(s3, s2, j + 6);
+    core(s0, s3, j + 7);
+    __syncwarp();  // every lane's reads of the group are ordered before lane 0's release
+    if (lane == 0) st_release_shared(consumed, (unsigned)(j / kGtGroup) + 1u);
+    const unsigned w = (unsigned)nx + 1u;
+    const unsigned mism = (f0 ^ w) | (f1 ^ (w + 1)) | (f2 ^ (w + 2)) | (f3 ^ (w + 3)) |
+                          (f4 ^ (w + 4)) | (f5 ^ (w + 5)) | (f6 ^ (w + 6)) | (f7 ^ (w + 7));
+    if (mism != 0) {  // rare: the producers are behind; block by block then
+      for (int i = 0; i < kGtGroup; ++i) await(nx + i, 0u);
+    } else {
+      fence_acquire_cta();
     }
-    int i = 0;
-    while (ok && i + 2 < n_full) {
-      ok = wait_stage(i + 1);
-      if (!ok) break;
-      FG_GIANT_PRODUCTS(i + 1, qa, qb);
-      FG_GIANT_CHAIN(pa, pb);
-      release_stage(i + 1);
-      ok = wait_stage(i + 2);
-      if (!ok) break;
-      FG_GIANT_PRODUCTS(i + 2, pa, pb);
-      FG_GIANT_CHAIN(qa, qb);
-      release_stage(i + 2);
-      i += 2;
-    }
-    // stage i is in (pa, pb); at most one more full stage follows
-    if (ok && i + 1 < n_full) {
-      ok = wait_stage(i + 1);
-      if (ok) {
-        FG_GIANT_PRODUCTS(i + 1, qa, qb);
-        FG_GIANT_CHAIN(pa, pb);
-        release_stage(i + 1);
-        FG_GIANT_CHAIN(qa, qb);
-      }
-    } else if (ok) {
-      FG_GIANT_CHAIN(pa, pb);
-    }
+    core(s1, s0, j + 8);
+    core(s2, s1, j + 9);
+    core(s3, s2, j + 10);
   }
-#undef FG_GIANT_PRODUCTS
-#undef FG_GIANT_CHAIN
-  if (ok && n_full < n_stages) {  // the ragged last stage
-    ok = wait_stage(n_full);
-    if (ok) {
-      heavy_consume_stage<VEC>(xs[n_full & (kGtSlots - 1)], val_s[n_full & (kGtSlots - 1)],
-                               deg - n_full * kHvEdges, lane, acc_a, acc_b);
-      release_stage(n_full);
-    }
+  // the tail: fewer than two groups of full blocks are left
+  seen = peek(j + 3);
+  for (; j < n_full; j += 4) {
+    step(j, s0, s3);
+    step(j + 1, s1, s0);
+    step(j + 2, s2, s1);
+    step(j + 3, s3, s2);
   }
-  if (!ok) {
+  if (n_full < n_blocks) {  // the ragged last block, straight from shared memory
+    await(n_full, 0u);
+    const float* src = prod[n_full & (kGtRing - 1)][lane];
+    const int cnt = deg - n_full * kHvEdges;
+    for (int e = 0; e < cnt; ++e) acc = __fadd_rn(acc, src[(((e >> 2) ^ swz) << 2) | (e & 3)]);
+  }
+  if (__any_sync(kFull, gave_up)) {
     if (lane == 0) atomicExch(status, kGtErrConsumerTimeout);
     return;  // the row is not written; the host sees the status
   }
-  heavy_store_row<VEC>(Y, (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
+  heavy_store_row<1>(Y, (size_t)row * F + (size_t)sub * 32, lane, acc, 0.f);
 }
 
 // Fallback for any feat_len / alignment: one warp per row, lanes over features.
@@ -516,7 +624,7 @@ struct fg_spmm_plan {
   int feat_len = 0;
   bool vector_ok = false;  // feat_len % 32 == 0
   int slab_w = 0;          // floats per light item (32, 64 or 128)
-  int heavy_vec = 1;       // floats per lane of the heavy / giant kernels (1 or 2)
+  int heavy_vec = 1;       // floats per lane of the heavy kernel (1 or 2)
   int heavy_threshold = 0, giant_threshold = 0;
   // rows sorted by degree, descending: [0, n_giant) giant, then n_heavy heavy, then light
   int n_giant = 0, n_heavy = 0, n_light = 0;
@@ -531,7 +639,11 @@ struct fg_spmm_plan {
 namespace fg {
 
 constexpr int kDefaultHeavyThreshold = 2048;
-constexpr int kDefaultGiantThreshold = 32768;
+constexpr int kMinGiantThreshold = 4096;
+// Measured on B200 (1965 MHz, feat_len 64, the 114.6 M-edge power-law graph): the whole
+// SpMM moves 50 (nonzero, 32-float slab) pairs per cycle on 148 SMs; the heavy kernel
+// walks one row at 47 cycles per nonzero, the giant kernel at 6.7.
+constexpr double kCyclesPerNnzSlab = 0.0197, kHeavyCyclesPerNnz = 47.0, kGiantCyclesPerNnz = 6.7;
 
 static void plan_release(fg_spmm_plan* p) {
   if (!p) return;
@@ -589,10 +701,6 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
   p->feat_len = feat_len;
   p->max_deg = max_deg;
   p->heavy_threshold = heavy_threshold > 0 ? heavy_threshold : kDefaultHeavyThreshold;
-  // An explicit threshold (tests use tiny ones) also scales the giant class down.
-  p->giant_threshold =
-      heavy_threshold > 0 ? std::min(kDefaultGiantThreshold, 16 * heavy_threshold)
-                          : kDefaultGiantThreshold;
   p->vector_ok = (feat_len % 32 == 0);
 
   DeviceGuard guard(device);
@@ -615,6 +723,22 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
   FG_PLAN_TRY(cudaDeviceGetAttribute(&p->n_sms, cudaDevAttrMultiProcessorCount, device));
   p->slab_w = choose_slab_width(feat_len, n_cols, p->l2_bytes);
   p->heavy_vec = (p->slab_w % 64 == 0) ? 2 : 1;
+  {
+    // Giant class: the rows whose add chain, walked by the heavy kernel's single warp,
+    // would last more than half of the call.  The call is estimated as the longer of
+    // its throughput time and the longest row's chain in the giant kernel; a shard of
+    // a multi-GPU run has less of the former, so more of its rows turn giant.  The
+    // giant kernel gives an SM to 32 floats of one row, so it is kept for such rows.
+    const double t_throughput = (double)p->nnz * (feat_len / 32.0) * kCyclesPerNnzSlab * 148.0 /
+                                std::max(1, p->n_sms);
+    const double t_call = std::max(t_throughput, (double)max_deg * kGiantCyclesPerNnz);
+    const double by_time = 0.5 * t_call / kHeavyCyclesPerNnz;
+    int64_t thr = (int64_t)std::min(by_time, 1e9);
+    thr = std::max<int64_t>(thr, kMinGiantThreshold);
+    // an explicit heavy threshold (tests use tiny ones) scales the giant class down with it
+    if (heavy_threshold > 0) thr = std::min<int64_t>(thr, 16 * (int64_t)heavy_threshold);
+    p->giant_threshold = (int)std::max<int64_t>(thr, p->heavy_threshold);
+  }
 
   if (p->vector_ok && n_rows > 0) {
     // Stable counting sort of the rows by degree, descending: the hardware
@@ -637,7 +761,8 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
     };
     // Giant class: rows over the giant threshold, but no more (row, slab) CTAs
     // than SMs -- a giant CTA wants an SM's worth of copy bandwidth to itself.
-    const int64_t giant_cap = std::max<int64_t>(1, p->n_sms / (feat_len / (32 * p->heavy_vec)));
+    // and no more giant CTAs (row, 32-float slab) than fit a 32-bit grid
+    const int64_t giant_cap = (int64_t)INT32_MAX / std::max(1, feat_len / 32);
     int64_t k = 0;
     while (k < n_rows && k < giant_cap && degree_at(k) > p->giant_threshold) p->giant_nnz += degree_at(k++);
     p->n_giant = (int)k;
@@ -653,12 +778,9 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
       FG_PLAN_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
       FG_PLAN_TRY(cudaEventCreateWithFlags(&p->fork_ev, cudaEventDisableTiming));
       if (p->n_giant > 0) {
-        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_giant_kernel<1>,
+        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_giant_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         giant_smem_bytes<1>()));
-        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_giant_kernel<2>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         giant_smem_bytes<2>()));
+                                         kGtSmemBytes));
         FG_PLAN_TRY(cudaStreamCreateWithPriority(&p->aux_giant, cudaStreamNonBlocking, hi));
         FG_PLAN_TRY(cudaEventCreateWithFlags(&p->join_giant, cudaEventDisableTiming));
         FG_PLAN_TRY(cudaMalloc(&p->status_dev, sizeof(int)));
@@ -720,14 +842,14 @@ extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t b
              "slab_w=%d | light: %d rows (deg<=%d) -> spmm_light_kernel<G=%d> grid=%lld x 256 thr | "
              "heavy: %d rows (deg<=%d), %lld nnz -> spmm_heavy_kernel<VEC=%d> grid=%lld x 32 thr, "
              "%d-stage cp.async ring, own stream | giant: %d rows, %lld nnz -> "
-             "spmm_giant_kernel<VEC=%d> grid=%lld x %d thr (%d producer warps + 1 consumer, "
-             "%d-slot ring, mbarriers), own stream",
+             "spmm_giant_kernel grid=%lld x %d thr (%d producer warps + 1 consumer, "
+             "%d-block ring of products, flag words), own stream",
              (long long)p->n_rows, (long long)p->n_cols, (long long)p->nnz, p->feat_len,
              (long long)p->max_deg, p->l2_bytes, p->slab_w, p->n_light, p->heavy_threshold, G,
              (light_items + 256 / G - 1) / (256 / G), p->n_heavy, p->giant_threshold,
              (long long)p->heavy_nnz, p->heavy_vec, (long long)p->n_heavy * hv_slabs, kHvXSlots,
-             p->n_giant, (long long)p->giant_nnz, p->heavy_vec, (long long)p->n_giant * hv_slabs,
-             32 * kGtWarps, kGtProducers, kGtSlots);
+             p->n_giant, (long long)p->giant_nnz, (long long)p->n_giant * (p->feat_len / 32),
+             32 * kGtWarps, kGtProducers, kGtRing);
   } else {
     snprintf(buf, (size_t)buf_len,
              "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d | spmm_generic_kernel "
@@ -796,16 +918,11 @@ extern "C" int fg_spmm_csr_f32_multi(const fg_spmm_plan* p, const int32_t* indpt
   if (p->fork_ev) FG_CUDA_TRY(cudaEventRecord(p->fork_ev, st));
   if (p->n_giant > 0) {
     FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_giant, p->fork_ev, 0));
-    const unsigned grid = (unsigned)(p->n_giant * hv_slabs);
-    const unsigned threads = 32 * kGtWarps;
-    if (p->heavy_vec == 2)
-      spmm_giant_kernel<2><<<grid, threads, giant_smem_bytes<2>(), p->aux_giant>>>(
-          indptr, indices, vals, x, y, p->rows_dev, p->n_giant, p->slab_w / slab, p->feat_len,
-          p->status_dev);
-    else
-      spmm_giant_kernel<1><<<grid, threads, giant_smem_bytes<1>(), p->aux_giant>>>(
-          indptr, indices, vals, x, y, p->rows_dev, p->n_giant, p->slab_w / slab, p->feat_len,
-          p->status_dev);
+    // one CTA per (row, 32-float slab), whatever the heavy kernel's slab is
+    const unsigned grid = (unsigned)(p->n_giant * (p->feat_len / 32));
+    spmm_giant_kernel<<<grid, 32 * kGtWarps, kGtSmemBytes, p->aux_giant>>>(
+        indptr, indices, vals, x, y, p->rows_dev, p->n_giant, p->slab_w / 32, p->feat_len,
+        p->status_dev);
     FG_CUDA_TRY(cudaGetLastError());
     FG_CUDA_TRY(cudaEventRecord(p->join_giant, p->aux_giant));
   }

@@ -19,9 +19,9 @@
 //       shared memory with cp.async rings, which takes the gather latency off
 //       the sequential add chain.
 //   * giant rows (the few whose chain would outlast the rest of the call) ->
-//       spmm_giant_kernel: one CTA per (row, 32-float slab); six producer warps
+//       spmm_giant_kernel: one CTA per (row, 32-float slab); nine producer warps
 //       gather, multiply and store transposed products into a shared-memory
-//       ring, one consumer warp only adds, in order, at 6.7 cycles per nonzero
+//       ring, one consumer warp only adds, in order, at 5.5 cycles per nonzero
 //       (the dependent fp32 add alone takes 4.2).  The longest row bounds the
 //       whole call -- its sum is one dependent chain.
 //   * anything the vector paths cannot take (feat_len not a multiple of 32,
@@ -275,17 +275,12 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   heavy_store_row<VEC>(Y, (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
 }
 
-constexpr int kGtWarps = 8;       // warps per CTA; warp 0 consumes, warp 4 retires
-constexpr int kGtProducers = 6;   // producer warps per CTA (warps 1, 2, 3, 5, 6, 7)
-constexpr int kGtGroup = 8;       // 32-nonzero blocks per group: one barrier hand-over per group
-constexpr int kGtGroups = 4;      // ring of groups (power of two)
+constexpr int kGtWarps = 12;      // warps per CTA; warp 0 consumes, warps 4 and 8 retire
+constexpr int kGtProducers = 9;   // producer warps per CTA (the warps with id % 4 != 0)
+constexpr int kGtGroup = 16;      // 32-nonzero blocks per group: one hand-over per group
+constexpr int kGtGroups = 3;      // ring of groups
 constexpr int kGtRing = kGtGroup * kGtGroups;  // blocks in the ring
-constexpr unsigned kGtMaxPolls = 1u << 20;     // bound of a spinning barrier wait (tests)
-// A parity wait can only tell a barrier's current phase from the previous one, so
-// every warp has to look at every phase of every barrier it waits on.  A
-// producer's consecutive blocks are kGtProducers apart; with no more producers
-// than blocks in a group it enters every group of the row, one after the other.
-static_assert(kGtProducers <= kGtGroup, "a producer may not skip a group");
+constexpr unsigned kGtMaxPolls = 1u << 20;     // bound of every wait for a flag
 constexpr int kGtErrProducerTimeout = 1, kGtErrConsumerTimeout = 2;
 constexpr int kGtSmemBytes = kGtRing * kHvEdges * 32 * 4   // products, [block][feature][nonzero]
                              + (kGtRing + 4) * 4;          // one flag per ring block, group counter
@@ -296,28 +291,39 @@ constexpr int kGtSmemBytes = kGtRing * kHvEdges * 32 * 4   // products, [block][
 // all 32 banks.
 __device__ __forceinline__ int giant_swizzle(int f) { return ((f >> 2) ^ f) & 7; }
 
-// One CTA per (giant row, 32-float slab): a consumer warp and six producer warps.
+// One CTA per (giant row, 32-float slab): a consumer warp and nine producer warps.
 //
 // The sum of one row is a dependent chain (CSR order, one accumulator per
 // feature), so the longest row bounds the whole SpMM -- on several GPUs even more
 // so, because the chain does not shrink with the shard -- and everything but the
-// add itself has to stay off that chain.  Measured, in cycles per block of 32
-// nonzeros: a lone warp gathering by cp.async 1500 (it keeps only a few copies
-// outstanding); a consumer that reads segments from shared memory, multiplies and
-// adds 290, and 450 beside busy producer warps; adds of ready products from
-// registers 135 -- the chain bound, 4.2 cycles per add; one mbarrier test by a
-// whole warp 180 (the 32 lanes' accesses to the one barrier word serialise, and
-// the instruction that takes the verdict stalls the warp whatever comes after),
-// by one lane 50.  So: producer w takes blocks w, w+6, w+12, ... of the row; it
-// gathers the X segments straight into registers (16-byte loads, three blocks in
-// flight), multiplies by the values and stores the PRODUCTS into the ring; the
-// consumer keeps the next three blocks in registers (lane = feature) while it
-// adds the current one, the loads alternating with the adds in one basic block.
-// Barriers work on groups of 8 blocks and are touched by lane 0 only: "full"
-// counts the 8 blocks' producers, "empty" is the consumer's hand-back once the
-// group sits in its registers.  Warp 4 retires at once: the consumer shares its
-// scheduler with nobody.  Every wait is a bounded poll; a wait that gives up
-// records a code in *status and the warp leaves.
+// add itself has to stay off that chain: 4.2 cycles per nonzero is the dependent
+// fp32 add alone.  What the measurements said, in cycles per block of 32 nonzeros
+// (the chain bound is 135):
+//   * a lone warp gathering by cp.async: 1500 (it keeps only a few copies
+//     outstanding), so the gathers need several warps;
+//   * a consumer that reads X segments from shared memory, multiplies and adds:
+//     290 alone, 450 beside busy producers -- 32 four-byte loads, 32 multiplies
+//     and the adds do not fit the chain's issue gaps; 8 sixteen-byte loads of
+//     ready products do (139), hence products stored TRANSPOSED;
+//   * an mbarrier test: 180 by a whole warp (32 lanes on one word), 50 to 100 by
+//     one lane, and the instruction that takes the verdict out of the predicate
+//     stalls the warp at once; a flag word read with a plain load can be read a
+//     step before it is looked at.  Hence flag words (release / acquire), and a
+//     hand-over only once per group of 16 blocks;
+//   * a warp has six scoreboards for all its loads and shuffles in flight, so a
+//     wait for a quick result (a shuffle) also waits for whatever slow load shares
+//     its scoreboard: software pipelines across batches of gathers ran at one
+//     memory latency per step whatever their depth.  Hence batches.
+// Producer w takes blocks w, w+9, w+18, ... of the row, three per batch: all the
+// batch's shuffles (each lane's 8 columns and values out of the warp's coalesced
+// copy), then its 24 gathers of 16 bytes and the next batch's columns / values, then,
+// per block, the multiplies, the lane's 8x4 tile transposed in registers, 8
+// sixteen-byte stores into the ring block and the block's flag.  The consumer (lane =
+// feature) holds the next three blocks in registers while it adds the current one,
+// loads alternating with adds in one basic block; it checks a whole group's flags at
+// once and hands a group back when its last block sits in registers.  Result: 5.5
+// cycles per nonzero (14.3 with row-major segments and per-block mbarriers).
+// Every wait is a bounded poll; a wait that gives up is recorded in *status.
 __global__ void __launch_bounds__(32 * kGtWarps)
 spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
@@ -342,9 +348,13 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   const int n_blocks = (deg + kHvEdges - 1) / kHvEdges;  // incl. a ragged last one
 
   if (threadIdx.x <= kGtRing) ready[threadIdx.x] = 0;  // the last one is *consumed
+  static_assert(kGtRing < 32 * kGtWarps && kGtGroup % 4 == 0 && kGtGroup >= 8, "ring / group shape");
   __syncthreads();
 
-  if (warp == 4) return;  // leave the consumer's scheduler alone
+  // Warps are dealt to the SM's four schedulers round-robin by id: warps 4 and 8 would
+  // share the consumer's and retire at once (measured: 5.5 cycles per nonzero this way,
+  // 6.3 with producers on the consumer's scheduler).
+  if (warp > 0 && (warp & 3) == 0) return;
   if (warp > 0) {
     // ------------------------------------------------------------ producer --
     const int* ind = indices + beg;
@@ -385,7 +395,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
       }
     };
     bool ok = true;
-    int entered = -1;  // last group whose "empty" barrier this warp has passed
+    int entered = -1;  // last group this warp has found handed back
     auto emit = [&](int u, const float (&vs)[8], const float4 (&x)[8]) {
       const int b = pw + u * kGtProducers;
       const int grp = b / kGtGroup;
@@ -412,7 +422,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
       }
       // the lane holds an 8-nonzero x 4-feature tile: transposed in registers, it
       // leaves as 8 quads (one feature, 4 consecutive nonzeros each)
-      float(*pt)[kHvEdges] = prod[b & (kGtRing - 1)];
+      float(*pt)[kHvEdges] = prod[b % kGtRing];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int q = (g8 >> 2) + h;  // quad of nonzeros g8 + 4h .. g8 + 4h + 3
@@ -426,7 +436,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
             make_float4(pr[4 * h].w, pr[4 * h + 1].w, pr[4 * h + 2].w, pr[4 * h + 3].w);
       }
       __syncwarp();  // every lane's stores are ordered before lane 0's release
-      if (lane == 0) st_release_shared(&ready[b & (kGtRing - 1)], (unsigned)b + 1u);
+      if (lane == 0) st_release_shared(&ready[b % kGtRing], (unsigned)b + 1u);
     };
     // Batches of three blocks.  A warp has six scoreboards for all its loads and
     // shuffles in flight, so a wait for any one result tends to wait for the newest
@@ -434,7 +444,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     // when something quick is waited for: (1) all shuffles of the batch (columns and
     // values per lane), (2) all 24 gathers, the next batch's columns / values (they
     // stream from DRAM, behind an L2 prefetch eight batches ahead) -- one exposed
-    // latency for the lot -- (3) multiply, pass the barrier, store, three times.
+    // latency for the lot -- (3) multiply, wait for the ring block, store, three times.
     float4 xa[8], xb[8], xc[8];
     float vsa[8], vsb[8], vsc[8];
     int ca, cb, cc;
@@ -475,7 +485,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   // check, so that the check costs a compare; the fence behind a successful check
   // turns it into an acquire (every lane's loads of the block come after it).  A lane
   // whose bounded wait gives up only notes it; the warp looks at the notes at the end.
-  auto peek = [&](int j) { return ld_relaxed_shared(&ready[j & (kGtRing - 1)]); };
+  auto peek = [&](int j) { return ld_relaxed_shared(&ready[j % kGtRing]); };
   bool gave_up = false;
   auto await = [&](int j, unsigned seen) {
     const unsigned want = (unsigned)j + 1u;
@@ -495,7 +505,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   const int swz = giant_swizzle(lane);
   auto fetch = [&](int j, float4 (&s)[8]) {  // prologue only
     if (j >= n_full) return;
-    const float* src = prod[j & (kGtRing - 1)][lane];
+    const float* src = prod[j % kGtRing][lane];
 #pragma unroll
     for (int q = 0; q < 8; ++q) s[q] = *reinterpret_cast<const float4*>(src + ((q ^ swz) << 2));
     release_after(j);
@@ -504,7 +514,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   // basic block, alternating, so that the loads issue in the gaps of the dependent add
   // chain instead of ahead of it.
   auto core = [&](const float4 (&sa)[8], float4 (&sf)[8], int jf) {
-    const float* src = prod[jf & (kGtRing - 1)][lane];
+    const float* src = prod[jf % kGtRing][lane];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       sf[q] = *reinterpret_cast<const float4*>(src + ((q ^ swz) << 2));
@@ -538,52 +548,55 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     }
   };
 
-  float4 s0[8], s1[8], s2[8], s3[8];
+  float4 S[4][8];  // indexed by constants only (the loops below unroll fully): registers
   for (int i = 0; i < kGtGroup && i < n_full; ++i) await(i, 0u);  // group 0, block by block
-  fetch(0, s0);
-  fetch(1, s1);
-  fetch(2, s2);
-  // Whole groups: block j (a multiple of 8) .. j+2 sit in s0 .. s2 and group j/8 has been
-  // checked.  Eight steps add blocks j .. j+7 and read blocks j+3 .. j+10; the flags
-  // of the next group are read in steps 0-3 and checked, all at once, before step 5
-  // reads its first block; the group is handed back after step 4 has read its last.
+  fetch(0, S[0]);
+  fetch(1, S[1]);
+  fetch(2, S[2]);
+  // Whole groups: blocks j (a multiple of the group size) .. j+2 sit in S[0] .. S[2] and
+  // group j / kGtGroup has been checked.  Step s adds block j+s and reads block j+s+3.
+  // The next group's flags are read two per step in the first steps, folded into one
+  // word a step after they were read, and checked -- all at once, with the fence that
+  // makes the check an acquire -- before the step that reads the next group's first
+  // block; this group is handed back after the step that reads its last block.
   int j = 0;
   for (; j + 2 * kGtGroup <= n_full; j += kGtGroup) {
     const int nx = j + kGtGroup;
-    const unsigned f0 = peek(nx), f1 = peek(nx + 1);
-    core(s0, s3, j + 3);
-    const unsigned f2 = peek(nx + 2), f3 = peek(nx + 3);
-    core(s1, s0, j + 4);
-    const unsigned f4 = peek(nx + 4), f5 = peek(nx + 5);
-    core(s2, s1, j + 5);
-    const unsigned f6 = peek(nx + 6), f7 = peek(nx + 7);
-    core(s3, s2, j + 6);
-    core(s0, s3, j + 7);
-    __syncwarp();  // every lane's reads of the group are ordered before lane 0's release
-    if (lane == 0) st_release_shared(consumed, (unsigned)(j / kGtGroup) + 1u);
     const unsigned w = (unsigned)nx + 1u;
-    const unsigned mism = (f0 ^ w) | (f1 ^ (w + 1)) | (f2 ^ (w + 2)) | (f3 ^ (w + 3)) |
-                          (f4 ^ (w + 4)) | (f5 ^ (w + 5)) | (f6 ^ (w + 6)) | (f7 ^ (w + 7));
-    if (mism != 0) {  // rare: the producers are behind; block by block then
-      for (int i = 0; i < kGtGroup; ++i) await(nx + i, 0u);
-    } else {
-      fence_acquire_cta();
+    unsigned mism = 0, pk0 = 0, pk1 = 0;
+#pragma unroll
+    for (int s = 0; s < kGtGroup; ++s) {
+      if (s >= 1 && s <= kGtGroup / 2)
+        mism |= (pk0 ^ (w + 2 * (s - 1))) | (pk1 ^ (w + 2 * (s - 1) + 1));
+      if (s < kGtGroup / 2) {
+        pk0 = peek(nx + 2 * s);
+        pk1 = peek(nx + 2 * s + 1);
+      }
+      if (s == kGtGroup - 3) {
+        if (mism != 0) {  // rare: the producers are behind; block by block then
+          for (int i = 0; i < kGtGroup; ++i) await(nx + i, 0u);
+        } else {
+          fence_acquire_cta();
+        }
+      }
+      core(S[s & 3], S[(s + 3) & 3], j + 3 + s);
+      if (s == kGtGroup - 4) {
+        __syncwarp();  // every lane's reads of the group are ordered before lane 0's release
+        if (lane == 0) st_release_shared(consumed, (unsigned)(j / kGtGroup) + 1u);
+      }
     }
-    core(s1, s0, j + 8);
-    core(s2, s1, j + 9);
-    core(s3, s2, j + 10);
   }
   // the tail: fewer than two groups of full blocks are left
   seen = peek(j + 3);
   for (; j < n_full; j += 4) {
-    step(j, s0, s3);
-    step(j + 1, s1, s0);
-    step(j + 2, s2, s1);
-    step(j + 3, s3, s2);
+    step(j, S[0], S[3]);
+    step(j + 1, S[1], S[0]);
+    step(j + 2, S[2], S[1]);
+    step(j + 3, S[3], S[2]);
   }
   if (n_full < n_blocks) {  // the ragged last block, straight from shared memory
     await(n_full, 0u);
-    const float* src = prod[n_full & (kGtRing - 1)][lane];
+    const float* src = prod[n_full % kGtRing][lane];
     const int cnt = deg - n_full * kHvEdges;
     for (int e = 0; e < cnt; ++e) acc = __fadd_rn(acc, src[(((e >> 2) ^ swz) << 2) | (e & 3)]);
   }
@@ -642,8 +655,8 @@ constexpr int kDefaultHeavyThreshold = 2048;
 constexpr int kMinGiantThreshold = 4096;
 // Measured on B200 (1965 MHz, feat_len 64, the 114.6 M-edge power-law graph): the whole
 // SpMM moves 50 (nonzero, 32-float slab) pairs per cycle on 148 SMs; the heavy kernel
-// walks one row at 47 cycles per nonzero, the giant kernel at 6.7.
-constexpr double kCyclesPerNnzSlab = 0.0197, kHeavyCyclesPerNnz = 47.0, kGiantCyclesPerNnz = 6.7;
+// walks one row at 47 cycles per nonzero, the giant kernel at 5.6.
+constexpr double kCyclesPerNnzSlab = 0.0197, kHeavyCyclesPerNnz = 47.0, kGiantCyclesPerNnz = 5.6;
 
 static void plan_release(fg_spmm_plan* p) {
   if (!p) return;

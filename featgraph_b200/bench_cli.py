@@ -63,6 +63,9 @@ def main(argv=None):
     ap.add_argument("--vertices", type=int, default=0)
     ap.add_argument("--edges", type=int, default=0)
     ap.add_argument("--scale", type=int, default=24, help="R-MAT scale (2**scale vertices)")
+    ap.add_argument("--row-partitions", type=int, default=1,
+                    help="SDDMM: the reference's 2-D edge blocking (VanillaSDDMMx86's arguments)")
+    ap.add_argument("--col-partitions", type=int, default=1)
     args = ap.parse_args(argv)
     if args.target != "cuda":
         raise SystemExit("this backend ships the cuda target only (no x86 code path)")
@@ -84,6 +87,16 @@ def main(argv=None):
         feat_lens = [int(f) for f in args.feat_len.split(",")]
     adj = g.to_scipy() if args.kernel == "spmm" else None
     rows = g.coo_rows() if args.kernel == "sddmm" else None
+    cols = g.indices
+    if args.kernel == "sddmm" and (args.row_partitions > 1 or args.col_partitions > 1):
+        # the blocked edge order of util_partition_adj_coo_2d (row partition major, column
+        # partition minor, row-major inside a block), computed on the device
+        rows_per = max(-(-g.n_rows // args.row_partitions), 1)
+        cols_per = max(-(-g.n_cols // args.col_partitions), 1)
+        key = (rows // rows_per).to(torch.int64) * args.col_partitions + (cols // cols_per)
+        order = torch.argsort(key, stable=True)
+        rows, cols = rows[order].contiguous(), cols[order].contiguous()
+        del key, order
 
     for f in feat_lens:
         shape = (args.heads, f // args.heads) if args.heads > 1 else (f,)
@@ -94,7 +107,7 @@ def main(argv=None):
             alg = 4 * (n + 1) + 8 * nnz + 4 * nnz * f + 4 * n * f
         else:
             y2 = graphs.normal_features(g.n_rows, shape, graphs.FEAT2_SEED, device)
-            op = ShardedSDDMM(rows, g.indices, n, g.n_cols, shape, device)
+            op = ShardedSDDMM(rows, cols, n, g.n_cols, shape, device)
             call = lambda: op.run(x, y2)                   # noqa: E731
             alg = 8 * nnz + 8 * nnz * f + 4 * nnz * args.heads
         for _ in range(3):
@@ -117,6 +130,7 @@ def main(argv=None):
             print(json.dumps({
                 "kernel": args.kernel, "graph": source, "rows": n, "nnz": nnz, "feat_len": f,
                 "heads": args.heads, "n_gpus": world, "num_runs": args.num_runs,
+                "partitions": [args.row_partitions, args.col_partitions],
                 "ms": round(ms, 4), "gflops": round(2.0 * nnz * f / ms / 1e6, 1),
                 "alg_gbs": round(alg / ms / 1e6, 1),
                 "frac_of_8TBs": round(alg / ms / 1e6 / NOMINAL_HBM_GBS, 4),

@@ -184,9 +184,12 @@ class SDDMMbase(object):
         return int(_lib.load().fg_sddmm_num_launches(self._adj_row_indices.shape[0],
                                                      a["feat_len"], a["num_heads"]))
 
+    _cuda_partitioning = False   # the reference's cuda class forces one partition
+
     @property
     def edge_mapping(self):
-        assert self._target != "cuda", "no graph partitioning on cuda, no edge_mapping"
+        assert self._target != "cuda" or self._cuda_partitioning, \
+            "no graph partitioning on cuda, no edge_mapping"
         assert self._num_row_partitions > 1 or self._num_col_partitions > 1, \
             "no graph partitioning, no edge_mapping"
         return self._edge_mapping
@@ -217,6 +220,26 @@ class VanillaSDDMMcuda(SDDMMbase):
         self._ctx = gpu(self._device_id)
         self._compute_func = vanilla_sddmm
         self._schedule_func = schedule_vanilla_sddmm_cuda_tree_reduce
+
+
+class PartitionedSDDMMcuda(VanillaSDDMMcuda):
+    """The reference's 2-D edge blocking (sddmm.py:45-49, adj_partitioning.py:60-128) on the
+    GPU, where the reference's own cuda class forces a single partition (sddmm.py:180-181).
+
+    The edges are reordered block by block (row partition major, column partition minor, the
+    caller's order inside a block) exactly as ``VanillaSDDMMx86`` does, the same kernels run
+    over the reordered list, and -- as there -- position i of the output holds the edge that
+    ``edge_mapping`` maps back: ``out[edge_mapping]`` is in the caller's order.  Per-edge
+    results do not depend on the order, so they are bit-identical to the unpartitioned ones.
+    Column partitions confine a stretch of edges to a window of SrcFeat rows: when SrcFeat
+    exceeds L2 (feat_len >= 256 on the 232 965-vertex graph) the window's rows are then
+    gathered from L2 instead of DRAM.
+    """
+    _cuda_partitioning = True
+
+    def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1, device_id=0):
+        self._device_id = int(device_id)
+        SDDMMbase.__init__(self, adj_scipy, num_row_partitions, num_col_partitions)
 
 
 class VanillaSDDMMx86(SDDMMbase):

@@ -103,6 +103,9 @@ def test_cuda_classes_fail_loudly_without_a_gpu():
         VanillaSpMMcuda(adj)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         VanillaSDDMMcuda(adj)
+    from featgraph_b200.module import PartitionedSDDMMcuda
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        PartitionedSDDMMcuda(adj, num_col_partitions=2)
 
 
 def test_float64_adjacency_is_rejected_not_cast(monkeypatch):

@@ -237,3 +237,24 @@ def test_extra_outputs_receive_the_same_results(oracle, shape):
     assert np.array_equal(want.reshape(-1), bits(out).reshape(-1))
     for e in extra:
         assert np.array_equal(want.reshape(-1), bits(e.cpu().numpy()))
+
+
+@pytest.mark.parametrize("parts", [(1, 4), (3, 1), (2, 5)])
+@pytest.mark.parametrize("shape", [(64,), (4, 16)])
+def test_partitioned_edges_and_edge_mapping(oracle, parts, shape):
+    # the reference's 2-D blocking (x86 only there) on the GPU: the output is in blocked
+    # order and edge_mapping takes it back to the caller's order, bit for bit
+    from featgraph_b200.module import PartitionedSDDMMcuda
+    coo = random_csr(230, 190, 0.08, seed=41).tocoo()
+    src, dst = features((190,) + shape, seed=42), features((230,) + shape, seed=43)
+    heads = shape[0] if len(shape) == 2 else 1
+    m = PartitionedSDDMMcuda(coo, num_row_partitions=parts[0], num_col_partitions=parts[1])
+    m.build([te.placeholder(src.shape), te.placeholder(dst.shape)], {}, {"num_cuda_blocks": 64})
+    out = m.run([nd.array(src, m.ctx), nd.array(dst, m.ctx)]).asnumpy()
+    want = oracle.sddmm_coo_f32(coo.row, coo.col, src, dst, num_heads=heads)
+    assert np.array_equal(bits(want.reshape(out.shape)), bits(out[m.edge_mapping]))
+    # blocked order: row partition major, column partition minor (adj_partitioning.py:60-128)
+    rp = m._adj_row_indices // -(-230 // parts[0])
+    cp = m._adj_col_indices // -(-190 // parts[1])
+    key = rp.astype(np.int64) * parts[1] + cp
+    assert np.all(np.diff(key) >= 0)

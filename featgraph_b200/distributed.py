@@ -4,8 +4,11 @@ The reference is single-device (python/featgraph/module/spmm.py:218, sddmm.py:18
 is the multi-GPU extension: SpMM is split into contiguous destination-row blocks that
 hold about nnz / world nonzeros each, SDDMM into equal contiguous edge ranges.  The
 dense features are replicated on every rank; each rank computes its block straight into
-its slice of a full-size output and the slices are exchanged with an all-gather, so every
-rank ends up with the whole result (what a following GNN layer needs).
+its slice of a full-size output, and every rank ends up with the whole result (what a
+following GNN layer needs).  On GPUs the full-size outputs live in symmetric memory and
+the kernels store each finished row / edge result into every peer's copy themselves
+(plain stores over NVLink, bracketed by two device-side barriers per call); where that
+cannot be set up the slices are exchanged with NCCL collectives instead.
 
 The classes take an already initialised process group (NCCL on GPUs).  ``make_local``
 is the only place that touches a device kernel, so host-side logic (bounds, sub-matrix
@@ -125,6 +128,10 @@ class ShardedSpMM(object):
         return "none" if self.world == 1 else ("peer_stores" if self._symm is not None else "nccl")
 
     def compute_local(self, x):
+        if self._symm is not None:
+            # peers store into this rank's output: they may start only when this rank's
+            # stream has passed everything that read the previous result
+            self._symm.barrier()
         self._local(x)
 
     def gather(self):
@@ -230,6 +237,8 @@ class ShardedSDDMM(object):
         return "none" if self.world == 1 else ("peer_stores" if self._symm is not None else "nccl")
 
     def compute_local(self, src, dst):
+        if self._symm is not None:
+            self._symm.barrier()   # as in ShardedSpMM.compute_local
         if self.edge_hi > self.edge_lo:
             self._local(src, dst)
 

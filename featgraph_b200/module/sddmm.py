@@ -239,6 +239,13 @@ class PartitionedSDDMMcuda(VanillaSDDMMcuda):
 
     def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1, device_id=0):
         self._device_id = int(device_id)
+        if num_row_partitions > 1 or num_col_partitions > 1:
+            # the reference's utility converts through CSR, which merges duplicate edges
+            # and adds up their ids (adj_partitioning.py:92-95): refuse instead
+            coo = adj_scipy if adj_scipy.format == "coo" else adj_scipy.tocoo()
+            key = coo.row.astype(np.int64) * int(coo.shape[1]) + coo.col
+            if np.unique(key).shape[0] != key.shape[0]:
+                raise ValueError("edge blocking needs a duplicate-free edge list")
         SDDMMbase.__init__(self, adj_scipy, num_row_partitions, num_col_partitions)
 
 

@@ -258,3 +258,6 @@ def test_partitioned_edges_and_edge_mapping(oracle, parts, shape):
     cp = m._adj_col_indices // -(-190 // parts[1])
     key = rp.astype(np.int64) * parts[1] + cp
     assert np.all(np.diff(key) >= 0)
+    dup = sp.coo_matrix((np.ones(3, np.float32), ([1, 1, 2], [3, 3, 0])), shape=(230, 190))
+    with pytest.raises(ValueError, match="duplicate-free"):
+        PartitionedSDDMMcuda(dup, num_col_partitions=2)

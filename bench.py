@@ -243,7 +243,8 @@ def run_gpu(args):
 
     fused = not args.nccl_gather
     spmm = ShardedSpMM(adj, FEAT, device, fused_gather=fused)
-    sddmm = ShardedSDDMM(rows_dev, g.indices, n, g.n_cols, FEAT, device, fused_gather=fused)
+    sddmm = ShardedSDDMM(rows_dev, g.indices, n, g.n_cols, FEAT, device, fused_gather=fused,
+                         peer_mode=args.peer_mode)
     stream = torch.cuda.current_stream(device)
 
     def barrier():
@@ -365,7 +366,8 @@ def run_gpu(args):
             "config": {"workload": workload_name(g), "graph_seed": graphs.GRAPH_SEED,
                        "degree": g.degree_stats(), "parallelism":
                            "spmm: nnz-balanced row blocks; sddmm: edge ranges; x%d; outputs "
-                           "assembled by %s" % (world, spmm.gather_mode),
+                           "assembled by %s (spmm) / %s (sddmm)" % (world, spmm.gather_mode,
+                                                                    sddmm.gather_mode),
                        "l2": "adjacency streams (0.9 GB per kernel) exceed L2 between launches; "
                              "no explicit flush"},
             "e2e": {"value": round(e2e_value, 1), "unit": UNIT,
@@ -474,6 +476,8 @@ def main():
     ap.add_argument("--reference-budget", type=float, default=90.0,
                     help="seconds of CPU work for the whole --impl reference run")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--peer-mode", choices=["auto", "store", "push"], default="auto",
+                    help="how SDDMM results reach the peers (see ShardedSDDMM)")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="assemble outputs with NCCL collectives instead of peer stores")
     args = ap.parse_args()

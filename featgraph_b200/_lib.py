@@ -28,7 +28,7 @@ EXPORTED_SYMBOLS = (
     "fg_spmm_plan_create", "fg_spmm_plan_destroy", "fg_spmm_plan_describe",
     "fg_spmm_plan_num_launches", "fg_spmm_plan_status", "fg_spmm_csr_f32", "fg_spmm_csr_f32_host",
     "fg_spmm_csr_f32_noalloc", "fg_spmm_noalloc_max_rows", "fg_spmm_csr_f32_multi",
-    "fg_sddmm_coo_f32_multi",
+    "fg_sddmm_coo_f32_multi", "fg_sddmm_coo_f32_push",
     "fg_sddmm_coo_f32", "fg_sddmm_coo_f32_host", "fg_sddmm_num_launches", "fg_sddmm_describe",
     "fg_shard_rows_by_nnz", "fg_shard_edges",
 )
@@ -57,6 +57,8 @@ def load():
     lib.fg_spmm_csr_f32_multi.argtypes = [c_void] * 5 + [ctypes.POINTER(c_void), i32, c_void]
     lib.fg_sddmm_coo_f32_multi.argtypes = [c_void] * 4 + [ctypes.POINTER(c_void), i32, i64, i64,
                                                           i64, i32, i32, i32, c_void]
+    lib.fg_sddmm_coo_f32_push.argtypes = [c_void] * 5 + [ctypes.POINTER(c_void), i32, i64, i64,
+                                                         i64, i32, i32, i32, c_void]
     lib.fg_spmm_csr_f32_noalloc.argtypes = [c_void] * 5 + [i64, i64, i32, i32, c_void]
     lib.fg_sddmm_coo_f32.argtypes = [c_void] * 5 + [i64, i64, i64, i32, i32, i32, c_void]
     lib.fg_sddmm_coo_f32_host.argtypes = [c_void] * 8 + [i64, i64, i64, i32, i32, i32, c_void]

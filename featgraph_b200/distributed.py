@@ -180,7 +180,10 @@ class ShardedSDDMM(object):
     """
 
     def __init__(self, row, col, n_rows, n_cols, feat_shape, device, group=None,
-                 fused_gather=True):
+                 fused_gather=True, peer_mode="auto"):
+        """peer_mode (fused path only): 'store' -- the SDDMM kernel stores each result into
+        every peer's output itself; 'push' -- a copy kernel pushes finished pieces to the
+        peers while the next piece computes; 'auto' -- 'store' for two ranks, else 'push'."""
         self.group = group
         self.rank, self.world = _group_info(group)
         self.device = torch.device(device)
@@ -190,7 +193,8 @@ class ShardedSDDMM(object):
         self.num_heads = self.feat_shape[0] if len(self.feat_shape) == 2 else 1
         self.nnz = int(row.shape[0])
         # equal chunks (the last one padded) so that one all-gather assembles the output
-        self.chunk = (self.nnz + self.world - 1) // self.world if self.nnz else 0
+        # (a multiple of 32 edges, so that every rank's slice starts 16-byte aligned)
+        self.chunk = ((self.nnz + self.world - 1) // self.world + 31) // 32 * 32 if self.nnz else 0
         lo = min(self.rank * self.chunk, self.nnz)
         hi = min(lo + self.chunk, self.nnz)
         self.edge_lo, self.edge_hi = lo, hi
@@ -212,8 +216,11 @@ class ShardedSDDMM(object):
         self._local = self.make_local(row[lo:hi], col[lo:hi])
         if self._symm is not None:
             off = self.rank * self.chunk * self.num_heads * 4
+            self.peer_mode = ("store" if self.world == 2 else "push") if peer_mode == "auto" \
+                else peer_mode
             self.module.set_extra_outputs([int(p) + off for r, p in
-                                           enumerate(self._symm.buffer_ptrs) if r != self.rank])
+                                           enumerate(self._symm.buffer_ptrs) if r != self.rank],
+                                          push=self.peer_mode == "push")
             self._symm.barrier()
 
     def make_local(self, row_local, col_local):
@@ -234,7 +241,9 @@ class ShardedSDDMM(object):
 
     @property
     def gather_mode(self):
-        return "none" if self.world == 1 else ("peer_stores" if self._symm is not None else "nccl")
+        if self.world == 1:
+            return "none"
+        return ("peer_" + self.peer_mode) if self._symm is not None else "nccl"
 
     def compute_local(self, src, dst):
         if self._symm is not None:

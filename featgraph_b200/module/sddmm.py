@@ -105,14 +105,28 @@ class SDDMMbase(object):
                                                  out.attrs["num_heads"], buf, len(buf)))
         return buf.value.decode() + " | hints: %r" % (sched.hints,)
 
-    def set_extra_outputs(self, device_pointers):
-        """Also store every result at these device addresses (peer-mapped copies of this
-        edge range's output on other GPUs, at most 7): the multi-GPU path's fused all-gather."""
+    def set_extra_outputs(self, device_pointers, push=False):
+        """Also deliver every result to these device addresses (peer-mapped copies of this
+        edge range's output on other GPUs, at most 7): the multi-GPU path's fused all-gather.
+        push=False: the SDDMM kernel stores each result to all of them itself.  push=True:
+        the edge range is computed in pieces and a copy kernel pushes piece k to the peers
+        while piece k+1 computes (better with more than one peer: 4-byte results stored to
+        several peers from inside the kernel leave a GPU at ~360 GB/s only)."""
         self._extra_outputs = [int(p) for p in device_pointers]
+        self._push_outputs = bool(push)
 
     def _launch(self, src, dst):
         a = self._spec.attrs
         extra = getattr(self, "_extra_outputs", None)
+        if extra and getattr(self, "_push_outputs", False):
+            import ctypes
+            peers = (ctypes.c_void_p * len(extra))(*extra)
+            _lib.check(_lib.load().fg_sddmm_coo_f32_push(
+                ptr(self._adj_row_indices_tvm.torch), ptr(self._adj_col_indices_tvm.torch),
+                ptr(src), ptr(dst), ptr(self.out_tvm.torch), peers, len(extra),
+                self._adj_row_indices.shape[0], self._num_rows, self._num_cols, a["feat_len"],
+                a["num_heads"], self._ctx.device_id, current_stream_handle(self._ctx)))
+            return
         if extra:
             import ctypes
             outs = (ctypes.c_void_p * (1 + len(extra)))(self.out_tvm.torch.data_ptr(), *extra)

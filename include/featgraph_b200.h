@@ -152,6 +152,18 @@ int fg_sddmm_coo_f32_multi(const int32_t* row_dev, const int32_t* col_dev,
                            int64_t n_rows, int64_t n_cols, int32_t feat_len,
                            int32_t num_heads, int32_t device, void* stream);
 
+/* SDDMM of this GPU's edge range with the result also delivered to peers (multi-GPU; no
+ * counterpart in the reference, which is single-device: module/sddmm.py:185).  The edge
+ * list is cut into pieces; piece k is copied into the same position of every peer's
+ * buffer (peer-mapped device pointers, plain 16-byte stores over NVLink by a copy kernel
+ * on an internal second stream) while piece k+1 is computed on `stream`.  `stream` waits
+ * for the last copy before the call's work counts as done on it.  Asynchronous.
+ * n_peers = 0 is fg_sddmm_coo_f32. */
+int fg_sddmm_coo_f32_push(const int32_t* row_dev, const int32_t* col_dev, const float* src_dev,
+                          const float* dst_dev, float* out_dev, float* const* peer_outs,
+                          int32_t n_peers, int64_t nnz, int64_t n_rows, int64_t n_cols,
+                          int32_t feat_len, int32_t num_heads, int32_t device, void* stream);
+
 /* Same computation from HOST feature buffers (edge lists stay resident, as in
  * SDDMMbase.__init__, python/featgraph/module/sddmm.py:59-60). */
 int fg_sddmm_coo_f32_host(const int32_t* row_dev, const int32_t* col_dev,

@@ -58,10 +58,14 @@ def _worker(rank, world, port):
             assert spmm.module.device_status() == 0
             per_rank = np.diff(adj.indptr[spmm.bounds])
             assert per_rank.max() - per_rank.min() <= np.diff(adj.indptr).max()
-            for shape, heads in (((64,), 1), ((4, 16), 4)):
+            # peers get the results from the SDDMM kernel's own stores, or from the copy
+            # kernel that pushes finished pieces while the next piece computes
+            for shape, heads, peer_mode in (((64,), 1, "store"), ((64,), 1, "push"),
+                                            ((4, 16), 4, "push"), ((4, 16), 4, "auto")):
                 sd = ShardedSDDMM(rows, g.indices, g.n_rows, g.n_cols, shape, dev,
-                                  fused_gather=fused)
-                out = sd.run(y2.view((-1,) + shape), x.view((-1,) + shape))
+                                  fused_gather=fused, peer_mode=peer_mode)
+                for _ in range(2):
+                    out = sd.run(y2.view((-1,) + shape), x.view((-1,) + shape))
                 torch.cuda.synchronize(dev)
                 dist.barrier()
                 want = fg_oracle.sddmm_coo_f32(rows.cpu().numpy(), g.indices.cpu().numpy(),

@@ -9,7 +9,7 @@
 //
 // Rows are sorted by degree on the host (plan) and split into three classes,
 // each with its own kernel, launched on three streams so that they overlap:
-//   * light rows (deg <= 2048) -> spmm_light_kernel: a group of G = W/4 lanes
+//   * light rows (deg <= max(2048, call estimate / 550 cycles)) -> spmm_light_kernel: a group of G = W/4 lanes
 //       owns one (row, W-float feature slab); float4 gathers straight into
 //       registers, 8 in flight per lane, index/value tile fetched one iteration
 //       ahead; rows are served in descending degree so that the groups of a
@@ -657,6 +657,8 @@ constexpr int kMinGiantThreshold = 4096;
 // SpMM moves 50 (nonzero, 32-float slab) pairs per cycle on 148 SMs; the heavy kernel
 // walks one row at 47 cycles per nonzero, the giant kernel at 5.6.
 constexpr double kCyclesPerNnzSlab = 0.0197, kHeavyCyclesPerNnz = 47.0, kGiantCyclesPerNnz = 5.6;
+// light/heavy boundary = estimated call time in cycles / this (8192 nonzeros for a 4.5 M-cycle call)
+constexpr double kLightCyclesPerNnzOfCall = 550.0;
 
 static void plan_release(fg_spmm_plan* p) {
   if (!p) return;
@@ -746,6 +748,14 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
     const double t_throughput = (double)p->nnz * (feat_len / 32.0) * kCyclesPerNnzSlab * 148.0 /
                                 std::max(1, p->n_sms);
     const double t_call = std::max(t_throughput, (double)max_deg * kGiantCyclesPerNnz);
+    // Heavy class: the light kernel moves more nonzeros per SM-cycle than the heavy one
+    // (0.45 against 0.26) but walks a row at about one gather latency per 8 nonzeros, so it
+    // keeps every row whose walk fits well inside the call.  Measured on the full graph,
+    // ms per call by threshold: feat_len 64 -- 2048: 2.28, 4096: 2.27, 8192: 2.10, 16384:
+    // 2.19; feat_len 128 -- 2048: 4.93, 8192: 4.72, 16384: 4.53.
+    if (heavy_threshold <= 0)
+      p->heavy_threshold = (int)std::min<double>(
+          1 << 20, std::max<double>(kDefaultHeavyThreshold, t_call / kLightCyclesPerNnzOfCall));
     const double by_time = 0.6 * t_call / kHeavyCyclesPerNnz;
     int64_t thr = (int64_t)std::min(by_time, 1e9);
     thr = std::max<int64_t>(thr, kMinGiantThreshold);

@@ -9,7 +9,7 @@
 //
 // Rows are sorted by degree on the host (plan) and split into three classes,
 // each with its own kernel, launched on three streams so that they overlap:
-//   * light rows (deg <= max(2048, call estimate / 550 cycles)) -> spmm_light_kernel: a group of G = W/4 lanes
+//   * light rows (deg <= max(2048, call estimate / 1100 cycles)) -> spmm_light_kernel: a group of G = W/4 lanes
 //       owns one (row, W-float feature slab); float4 gathers straight into
 //       registers, 8 in flight per lane, index/value tile fetched one iteration
 //       ahead; rows are served in descending degree so that the groups of a
@@ -657,8 +657,8 @@ constexpr int kMinGiantThreshold = 4096;
 // SpMM moves 50 (nonzero, 32-float slab) pairs per cycle on 148 SMs; the heavy kernel
 // walks one row at 47 cycles per nonzero, the giant kernel at 5.6.
 constexpr double kCyclesPerNnzSlab = 0.0197, kHeavyCyclesPerNnz = 47.0, kGiantCyclesPerNnz = 5.6;
-// light/heavy boundary = estimated call time in cycles / this (8192 nonzeros for a 4.5 M-cycle call)
-constexpr double kLightCyclesPerNnzOfCall = 550.0;
+// light/heavy boundary = estimated call time in cycles / this (4096 nonzeros for a 4.5 M-cycle call)
+constexpr double kLightCyclesPerNnzOfCall = 1100.0;
 
 static void plan_release(fg_spmm_plan* p) {
   if (!p) return;
@@ -750,9 +750,11 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
     const double t_call = std::max(t_throughput, (double)max_deg * kGiantCyclesPerNnz);
     // Heavy class: the light kernel moves more nonzeros per SM-cycle than the heavy one
     // (0.45 against 0.26) but walks a row at about one gather latency per 8 nonzeros, so it
-    // keeps every row whose walk fits well inside the call.  Measured on the full graph,
-    // ms per call by threshold: feat_len 64 -- 2048: 2.28, 4096: 2.27, 8192: 2.10, 16384:
-    // 2.19; feat_len 128 -- 2048: 4.93, 8192: 4.72, 16384: 4.53.
+    // keeps every row whose walk fits well inside the call.  Measured on the full graph at
+    // feat_len 64, ms per call by threshold, with an SDDMM between the calls as in a GNN
+    // layer (X starts cold in L2): 2048: 2.36, 3072: 2.28, 4096: 2.28, 6144: 2.40, 8192:
+    // 2.43; back to back (X stays in L2) larger is better: 4096: 2.33, 8192: 2.13, 12288:
+    // 2.11.  The boundary is set for the first case.
     if (heavy_threshold <= 0)
       p->heavy_threshold = (int)std::min<double>(
           1 << 20, std::max<double>(kDefaultHeavyThreshold, t_call / kLightCyclesPerNnzOfCall));

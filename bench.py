@@ -40,7 +40,7 @@ UNIT = "GFLOP/s"
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload, from one
 # ncu capture (profiles/bench_full_size_launch_list_and_dram.md); other sizes report null.
-NCU_TRAFFIC_BYTES = {"spmm": 1921.3e6 + 205.3e6, "sddmm": 1920.2e6 + 886.1e6}
+NCU_TRAFFIC_BYTES = {"spmm": 1843.2e6 + 199.2e6, "sddmm": 1908.2e6 + 891.2e6}
 FALLBACK_HBM_GBS = 6650.0
 
 

@@ -219,10 +219,11 @@ static int sddmm_variant(int F, int H) {
 
 // Copies n floats of this GPU's results into the same position of every peer's buffer
 // (peer-mapped pointers): coalesced 16-byte loads and stores, a modest grid that leaves
-// the SMs to the SDDMM kernel running beside it.  Measured on 4 and 8 GPUs: 4-byte
-// results stored to the peers from inside the SDDMM kernel itself leave a GPU at only
-// ~360 GB/s and slow the kernel down threefold; this bulk form runs at NVLink speed
-// beside the next piece's compute.
+// the SMs to the SDDMM kernel running beside it.  An alternative to storing the results
+// to the peers from inside the SDDMM kernel, for callers whose slices of the peers'
+// buffers are not 128-byte aligned (a warp's 32 results then straddle two lines of the
+// peer's memory and the in-kernel stores leave a GPU at only ~360 GB/s; aligned, the
+// in-kernel stores are the faster form: 0.67 against 1.01 ms per SDDMM on 8 GPUs).
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 sddmm_push_kernel(const float* __restrict__ src, OutPtrs peers, long long offset, long long n) {

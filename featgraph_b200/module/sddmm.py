@@ -110,8 +110,8 @@ class SDDMMbase(object):
         edge range's output on other GPUs, at most 7): the multi-GPU path's fused all-gather.
         push=False: the SDDMM kernel stores each result to all of them itself.  push=True:
         the edge range is computed in pieces and a copy kernel pushes piece k to the peers
-        while piece k+1 computes (better with more than one peer: 4-byte results stored to
-        several peers from inside the kernel leave a GPU at ~360 GB/s only)."""
+        while piece k+1 computes.  Measured on 8 GPUs with 128-byte aligned slices: in-kernel
+        stores 0.67 ms per SDDMM, push 1.01 ms; on 2 GPUs 1.49 against 1.78 ms."""
         self._extra_outputs = [int(p) for p in device_pointers]
         self._push_outputs = bool(push)
 

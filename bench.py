@@ -38,9 +38,12 @@ FEAT = 64
 METRIC = "spmm_plus_sddmm_fp32_feat64_gflops"
 UNIT = "GFLOP/s"
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload, from one
-# ncu capture (profiles/bench_full_size_launch_list_and_dram.md); other sizes report null.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload on one GPU.
+# STATIC figures from one ncu capture (they do not follow later kernel changes until the
+# capture is repeated); other sizes and world sizes report null.
 NCU_TRAFFIC_BYTES = {"spmm": 1843.2e6 + 199.2e6, "sddmm": 1908.2e6 + 891.2e6}
+NCU_TRAFFIC_SOURCE = ("static: one ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of "
+                      "the full-size 1-GPU workload with the kernels of commit 6b594cb")
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -52,6 +55,37 @@ def spmm_alg_bytes(n_rows, nnz, f):
 def sddmm_alg_bytes(nnz, f, heads=1):
     """row + col + both gathered rows of every edge + out."""
     return 8 * nnz + 8 * nnz * f + 4 * nnz * heads
+
+
+def spmm_l2_bytes(n_rows, nnz, f):
+    """Bytes that have to cross the L2 -> SM path: structure, one gathered X row per nonzero,
+    and Y once."""
+    return 8 * nnz + 4 * nnz * f + 4 * n_rows * f
+
+
+def sddmm_l2_bytes(n_rows, nnz, f, heads=1):
+    """The same for SDDMM on a row-sorted edge list: the src row of every edge, but the dst
+    row only once per run of equal rows (bounded below by once per row), and the output."""
+    return 8 * nnz + 4 * nnz * f + 4 * n_rows * f + 4 * nnz * heads
+
+
+def host_threads():
+    """Threads the CPU legs use: the cores this process may run on, NOT the inherited
+    OMP_NUM_THREADS (torch.distributed.run exports OMP_NUM_THREADS=1 to every rank)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def config_block(n_rows, nnz, degree):
+    """`config` of the JSON line: identical in the GPU arm and the reference arm."""
+    return {"workload": ("powerlaw_chung_lu_zipf2.1 N=%d nnz=%d feat_len=%d fp32: CSR SpMM + "
+                         "COO SDDMM (synthetic stand-in for the Reddit graph)"
+                         % (n_rows, nnz, FEAT)),
+            "graph_seed": graphs.GRAPH_SEED, "degree": degree,
+            "l2": "inputs larger than L2: each kernel streams 0.9 GB of adjacency (7 x L2) "
+                  "between uses of anything; no explicit flush"}
 
 
 def measured_peak():
@@ -138,7 +172,8 @@ def cpu_oracle_rates(csr_host, rows_host, x_host, y2_host, budget_s):
     combined GFLOP/s plus a description of the sample."""
     from oracle import fg_oracle
     fg_oracle.build()
-    threads = fg_oracle.max_threads()
+    threads = host_threads()
+    fg_oracle.set_threads(threads)
     indptr, indices, vals = csr_host
     n_rows, nnz, f = indptr.shape[0] - 1, indices.shape[0], x_host.shape[1]
 
@@ -212,11 +247,98 @@ def workload_name(g):
             "(synthetic stand-in for the Reddit graph)" % (g.n_rows, g.nnz, FEAT))
 
 
+# ------------------------------------------------------------------------------ parity --
+
+def parity_check(adj, rows_dev, x, y2, spmm, sddmm, world, rank):
+    """Bit-for-bit comparison of sampled parts of the FULL outputs held by this rank --
+    its own block and the blocks written by its peers -- with the CPU oracle.
+
+    SpMM: the 24 longest rows, 3 000 random rows and the rows on both sides of every shard
+    boundary.  SDDMM: windows of 50 000 edges, one at the start of every rank's range (so
+    every writer is covered), one straddling every range boundary, and four random ones.
+    Returns (rows checked, edges checked, mismatching values)."""
+    from oracle import fg_oracle
+    fg_oracle.build()
+    fg_oracle.set_threads(max(1, host_threads() // world))
+    x_h, y2_h = x.cpu().numpy(), y2.cpu().numpy()
+    indptr = adj.indptr
+    deg = np.diff(indptr)
+    n_rows, nnz = adj.shape[0], int(adj.nnz)
+    rng = np.random.default_rng(1234)          # the same picks on every rank
+    near = np.concatenate([[b - 1, b] for b in spmm.bounds[1:-1]]) if world > 1 else []
+    picks = np.unique(np.concatenate([np.argsort(deg)[-24:], rng.integers(0, n_rows, 3000),
+                                      np.asarray(near, dtype=np.int64)]))
+    picks = picks[(picks >= 0) & (picks < n_rows)].astype(np.int64)
+    sub_ptr = np.concatenate(([0], np.cumsum(deg[picks]))).astype(np.int32)
+    sel = np.concatenate([np.arange(indptr[r], indptr[r + 1]) for r in picks])
+    want = fg_oracle.spmm_csr_f32(sub_ptr, adj.indices[sel], adj.data[sel], x_h,
+                                  n_cols=adj.shape[1])
+    got = spmm.out[torch.from_numpy(picks).to(spmm.out.device)].cpu().numpy()
+    bad = int((want.view(np.int32) != got.view(np.int32)).sum())
+
+    win = 50000
+    starts = [int(b) for b in sddmm.bounds[:-1]]
+    starts += [max(0, int(b) - win // 2) for b in sddmm.bounds[1:-1]]
+    starts += [int(v) for v in rng.integers(0, max(1, nnz - win), 4)]
+    rows_h = None
+    edges = 0
+    for s0 in sorted(set(starts)):
+        s1 = min(nnz, s0 + win)
+        if s1 <= s0:
+            continue
+        rows_h = rows_dev[s0:s1].cpu().numpy()
+        want = fg_oracle.sddmm_coo_f32(rows_h, adj.indices[s0:s1], y2_h, x_h, parallel=True)
+        got = sddmm.out[s0:s1].cpu().numpy()
+        bad += int((want.view(np.int32) != got.view(np.int32)).sum())
+        edges += s1 - s0
+    return int(picks.shape[0]), int(edges), bad
+
+
+# ---------------------------------------------------------------------- L2 gather peak --
+
+def l2_gather_peak(device, n_rows):
+    """GB/s at which the L2 -> SM path delivers gathered rows of a table that fits L2 (the
+    size of X at feat_len 64): the library's gather-only probe kernel, 256-byte and 128-byte
+    rows at pseudo-random indices, 16-byte loads, eight in flight per lane; CUDA events,
+    best of 5 after warm-up."""
+    import ctypes
+    from featgraph_b200 import _lib
+    lib = _lib.load()
+    table = torch.randn(n_rows, 64, device=device)
+    sink = torch.zeros(1, device=device)
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    stream = torch.cuda.current_stream(device)
+    out = {}
+    for row_floats in (64, 32):
+        groups_per_block = 256 // (row_floats // 4)
+        n_blocks, rows_per_group = sms * 8, 2048
+        rows_tbl = n_rows * 64 // row_floats
+
+        def launch():
+            _lib.check(lib.fg_gather_probe(
+                ctypes.c_void_p(table.data_ptr()), rows_tbl, row_floats, rows_per_group, n_blocks,
+                ctypes.c_void_p(sink.data_ptr()), device.index or 0,
+                ctypes.c_void_p(stream.cuda_stream)))
+        for _ in range(3):
+            launch()
+        best = None
+        for _ in range(5):
+            a = _mark(stream)
+            launch()
+            b = _mark(stream)
+            b.synchronize()
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+        total = n_blocks * groups_per_block * rows_per_group * row_floats * 4
+        out[row_floats] = total / (best * 1e-3) / 1e9
+    return out
+
+
 # ------------------------------------------------------------------------- our GPU arm --
 
 def run_gpu(args):
     import torch.distributed as dist
-    from featgraph_b200.distributed import ShardedSDDMM, ShardedSpMM
+    from featgraph_b200.distributed import OverlappedPair, ShardedSDDMM, ShardedSpMM
 
     rank, world, local = dist_env()
     if world != args.gpus:
@@ -230,10 +352,6 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
-        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; the contract of this
-        # script is one JSON line on stdout
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     g, x, y2 = make_inputs(args, device)
@@ -242,9 +360,11 @@ def run_gpu(args):
     n, nnz = g.n_rows, g.nnz
 
     fused = not args.nccl_gather
-    spmm = ShardedSpMM(adj, FEAT, device, fused_gather=fused)
+    spmm = ShardedSpMM(adj, FEAT, device, fused_gather=fused, peer_mode=args.peer_mode)
     sddmm = ShardedSDDMM(rows_dev, g.indices, n, g.n_cols, FEAT, device, fused_gather=fused,
                          peer_mode=args.peer_mode)
+    pair = OverlappedPair(spmm, sddmm)
+    overlap = args.schedule == "overlap"
     stream = torch.cuda.current_stream(device)
 
     def barrier():
@@ -253,6 +373,18 @@ def run_gpu(args):
         torch.cuda.synchronize(device)
 
     def step(events=None):
+        """One SpMM and one SDDMM.  'serial': one after the other on one stream, five marks
+        (SpMM kernels | its exchange | SDDMM kernel | its exchange).  'overlap': the SDDMM
+        on a second stream beside the SpMM, one barrier pair around both; four marks (SpMM
+        start / end on the main stream, SDDMM start / end on the side stream) between the
+        step's own start and end marks."""
+        if overlap:
+            marks = None if events is None else []
+            begin = _mark(stream) if events is not None else None
+            pair.run(x, y2, x, marks)            # SrcFeat (by col) = y2, DstFeat (by row) = x
+            if events is not None:
+                events.append([begin] + marks + [_mark(stream)])
+            return
         marks = []
         if events is not None:
             marks.append(_mark(stream))
@@ -262,7 +394,7 @@ def run_gpu(args):
         spmm.gather()
         if events is not None:
             marks.append(_mark(stream))
-        sddmm.compute_local(y2, x)          # SrcFeat (by col) = y2, DstFeat (by row) = x
+        sddmm.compute_local(y2, x)
         if events is not None:
             marks.append(_mark(stream))
         sddmm.gather()
@@ -285,11 +417,19 @@ def run_gpu(args):
         step(events)
     barrier()
     t1 = time.perf_counter()
-    if spmm.module.device_status() != 0:      # raises if a bounded device-side wait gave up
-        raise SystemExit("SpMM reported a device-side error")
+    spmm.device_status()                      # raises if a bounded device-side wait gave up
+    sddmm.device_status()
     total_ms = events[0][0].elapsed_time(events[-1][-1])
-    phases = np.array([[m[i].elapsed_time(m[i + 1]) for i in range(4)] for m in events])
+    if overlap:
+        # [spmm kernels, 0, sddmm kernel, 0]: each kernel's own duration while the other runs
+        phases = np.array([[m[1].elapsed_time(m[2]), 0.0, m[3].elapsed_time(m[4]), 0.0]
+                           for m in events])
+    else:
+        phases = np.array([[m[i].elapsed_time(m[i + 1]) for i in range(4)] for m in events])
     clocks = sampler.summary(t0, t1)
+
+    # ---- parity of what was just timed: sampled rows / edge windows of the full outputs ----
+    par_rows, par_edges, par_bad = parity_check(adj, rows_dev, x, y2, spmm, sddmm, world, rank)
 
     # ---- end to end from pinned host buffers, through run_host ----------------------------
     x_host = torch.empty((g.n_cols, FEAT), dtype=torch.float32, pin_memory=True).copy_(x)
@@ -309,6 +449,15 @@ def run_gpu(args):
     barrier()
     e2e_ms = a.elapsed_time(b)
     sampler.stop()
+    # what came back to the host is the same result (this rank's blocks)
+    e2e_bad = int((y_host[spmm.row_lo:spmm.row_hi].view(torch.int32)
+                   != spmm.out[spmm.row_lo:spmm.row_hi].cpu().view(torch.int32)).sum())
+    e2e_bad += int((o_host[sddmm.edge_lo:sddmm.edge_hi].view(torch.int32)
+                    != sddmm.out[sddmm.edge_lo:sddmm.edge_hi].cpu().view(torch.int32)).sum())
+
+    probe = None
+    if rank == 0 and not args.no_l2_probe:
+        probe = l2_gather_peak(device, n)
 
     if world > 1:
         t = torch.tensor([total_ms, e2e_ms], device=device, dtype=torch.float64)
@@ -317,6 +466,10 @@ def run_gpu(args):
         ph = torch.tensor(phases.mean(axis=0), device=device, dtype=torch.float64)
         dist.all_reduce(ph, op=dist.ReduceOp.MAX)
         phase_ms = ph.cpu().numpy()
+        pb = torch.tensor([par_bad, e2e_bad, par_rows, par_edges], device=device,
+                          dtype=torch.int64)
+        dist.all_reduce(pb, op=dist.ReduceOp.SUM)
+        par_bad, e2e_bad, par_rows, par_edges = (int(v) for v in pb)
     else:
         phase_ms = phases.mean(axis=0)
 
@@ -327,8 +480,9 @@ def run_gpu(args):
 
     if rank == 0:
         peak, peak_kind = measured_peak()
-        local_spmm_bytes = spmm_alg_bytes(spmm.row_hi - spmm.row_lo, spmm.local_nnz, FEAT)
-        local_sddmm_bytes = sddmm_alg_bytes(sddmm.edge_hi - sddmm.edge_lo, FEAT)
+        local_rows, local_edges = spmm.row_hi - spmm.row_lo, sddmm.edge_hi - sddmm.edge_lo
+        local_spmm_bytes = spmm_alg_bytes(local_rows, spmm.local_nnz, FEAT)
+        local_sddmm_bytes = sddmm_alg_bytes(local_edges, FEAT)
         spmm_ms, sddmm_ms = float(phase_ms[0]), float(phase_ms[2])
 
         default_size = (world == 1 and n == graphs.REDDIT_NUM_VERTICES
@@ -337,24 +491,36 @@ def run_gpu(args):
         def traffic(kernel):
             return int(NCU_TRAFFIC_BYTES[kernel]) if default_size else None
 
-        def roof(alg_bytes, ms, traffic):
+        def roof(alg_bytes, ms, traffic, l2_bytes):
             ach = alg_bytes / (ms * 1e-3) / 1e9
-            return {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s",
-                    "frac": round(ach / peak, 4), "peak_kind": peak_kind,
-                    "frac_of_nominal_8TBs": round(ach / NOMINAL_HBM_GBS, 4),
-                    "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": round(ms, 4),
-                    "traffic": traffic}
+            r = {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s",
+                 "frac": round(ach / peak, 4), "peak_kind": peak_kind,
+                 "frac_of_nominal_8TBs": round(ach / NOMINAL_HBM_GBS, 4),
+                 "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": round(ms, 4),
+                 "traffic": traffic,
+                 "traffic_source": NCU_TRAFFIC_SOURCE if traffic is not None else None}
+            if probe:
+                l2_ach = l2_bytes / (ms * 1e-3) / 1e9
+                r["roofline_l2"] = {
+                    "bound": "l2_gather", "bytes_per_launch": l2_bytes,
+                    "achieved": round(l2_ach, 1), "peak": round(probe[64], 1), "unit": "GB/s",
+                    "frac_l2": round(l2_ach / probe[64], 4),
+                    "peak_kind": "measured in this run: gather-only probe kernel, 256-byte rows "
+                                 "at random indices of a table the size of X (fits L2)",
+                    "peak_128_byte_rows": round(probe[32], 1)}
+            return r
 
         kernels = {
-            "spmm": dict(roof(local_spmm_bytes, spmm_ms, traffic("spmm")),
+            "spmm": dict(roof(local_spmm_bytes, spmm_ms, traffic("spmm"),
+                              spmm_l2_bytes(local_rows, spmm.local_nnz, FEAT)),
                          kernels="spmm_giant_kernel + spmm_heavy_kernel + spmm_light_kernel "
                                  "(three concurrent streams)",
                          gflops=round(2.0 * spmm.local_nnz * FEAT / (spmm_ms * 1e-3) / 1e9, 1),
                          gather_ms=round(float(phase_ms[1]), 4)),
-            "sddmm": dict(roof(local_sddmm_bytes, sddmm_ms, traffic("sddmm")),
+            "sddmm": dict(roof(local_sddmm_bytes, sddmm_ms, traffic("sddmm"),
+                               sddmm_l2_bytes(n, local_edges, FEAT)),
                           kernels="sddmm_tile_kernel",
-                          gflops=round(2.0 * (sddmm.edge_hi - sddmm.edge_lo) * FEAT
-                                       / (sddmm_ms * 1e-3) / 1e9, 1),
+                          gflops=round(2.0 * local_edges * FEAT / (sddmm_ms * 1e-3) / 1e9, 1),
                           gather_ms=round(float(phase_ms[3]), 4)),
         }
         dominant = "sddmm" if sddmm_ms >= spmm_ms else "spmm"
@@ -363,19 +529,29 @@ def run_gpu(args):
             "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(g), "graph_seed": graphs.GRAPH_SEED,
-                       "degree": g.degree_stats(), "parallelism":
-                           "spmm: nnz-balanced row blocks; sddmm: edge ranges; x%d; outputs "
-                           "assembled by %s (spmm) / %s (sddmm)" % (world, spmm.gather_mode,
-                                                                    sddmm.gather_mode),
-                       "l2": "adjacency streams (0.9 GB per kernel) exceed L2 between launches; "
-                             "no explicit flush"},
+            "config": config_block(n, nnz, g.degree_stats()),
+            "parallelism": "spmm: nnz-balanced row blocks; sddmm: edge ranges; x%d; outputs "
+                           "assembled by %s (spmm) / %s (sddmm); schedule: %s"
+                           % (world, spmm.gather_mode, sddmm.gather_mode,
+                              "SDDMM on a second stream beside the SpMM, one barrier pair per "
+                              "step; per-kernel times are each kernel's own start-to-end while "
+                              "the other runs" if overlap else
+                              "SpMM, then SDDMM, on one stream"),
             "e2e": {"value": round(e2e_value, 1), "unit": UNIT,
-                    "h2d_bytes_per_step": int(world * 3 * g.n_cols * FEAT * 4),
+                    "h2d_bytes_per_step": int(3 * g.n_cols * FEAT * 4),
                     "d2h_bytes_per_step": int(n * FEAT * 4 + nnz * 4),
-                    "ms_per_step": round(e2e_ms / e2e_steps, 3), "steps": e2e_steps},
-            "gpu_launches": int(args.steps * (spmm.num_launches() + sddmm.num_launches())),
+                    "ms_per_step": round(e2e_ms / e2e_steps, 3), "steps": e2e_steps,
+                    "note": "whole job: every replicated input crosses PCIe once (1/%d per rank, "
+                            "exchanged over NVLink), every rank downloads its own block" % world
+                            if world > 1 else "fg_*_host entry points, pinned host buffers"},
+            "gpu_launches": int(args.steps * (spmm.num_launches() + sddmm.num_launches()
+                                              + (0 if world == 1 or not fused else
+                                                 (2 if overlap else 4)))),
             "clocks": clocks,
+            "parity": {"spmm_rows": par_rows, "sddmm_edges": par_edges, "mismatches": par_bad,
+                       "e2e_mismatches": e2e_bad,
+                       "how": "bit-for-bit against the CPU oracle on every rank's copy of the "
+                              "full outputs, after the timed loop (sums over ranks)"},
             "roofline": dict(kernels[dominant], kernel=kernels[dominant]["kernels"]),
             "kernels": kernels,
             "cpu_baseline": None,
@@ -388,6 +564,9 @@ def run_gpu(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if par_bad or e2e_bad:
+        raise SystemExit("bench.py: %d sampled values differ from the oracle, %d host-side"
+                         % (par_bad, e2e_bad))
 
 
 def _mark(stream):
@@ -408,10 +587,12 @@ def run_reference(args):
     vals, rows = g.vals.cpu().numpy(), g.coo_rows().cpu().numpy()
     x_h, y2_h = x.cpu().numpy(), y2.cpu().numpy()
     nnz = g.nnz
+    degree = g.degree_stats()
     del g
     from oracle import fg_oracle
     fg_oracle.build()
-    threads = fg_oracle.max_threads()
+    threads = host_threads()
+    fg_oracle.set_threads(threads)
 
     # size the per-step sample from a probe so that warmup + steps fit the budget
     n_rows = indptr.shape[0] - 1
@@ -449,11 +630,9 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "powerlaw_chung_lu_zipf2.1 N=%d nnz=%d feat_len=%d fp32: CSR "
-                               "SpMM + COO SDDMM (synthetic stand-in for the Reddit graph)"
-                               % (n_rows, nnz, FEAT),
-                   "note": "CPU port of the reference's x86 kernels (TVM v0.7 cannot be "
-                           "installed); throughput on a bounded sample of the workload"},
+        "config": config_block(n_rows, nnz, degree),
+        "note": "CPU port of the reference's x86 kernels (TVM v0.7 cannot be installed); "
+                "throughput on a bounded sample of the workload, %d host threads" % threads,
         "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": threads,
                          "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0,
@@ -476,8 +655,13 @@ def main():
     ap.add_argument("--reference-budget", type=float, default=90.0,
                     help="seconds of CPU work for the whole --impl reference run")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--peer-mode", choices=["auto", "store", "push"], default="auto",
-                    help="how SDDMM results reach the peers (see ShardedSDDMM)")
+    ap.add_argument("--peer-mode", choices=["auto", "store", "mcast", "push"], default="auto",
+                    help="how results reach the peers (see featgraph_b200.distributed)")
+    ap.add_argument("--schedule", choices=["overlap", "serial"], default="serial",
+                    help="serial: SpMM then SDDMM on one stream; overlap: the SDDMM on a second "
+                         "stream beside the SpMM")
+    ap.add_argument("--no-l2-probe", action="store_true",
+                    help="skip the measurement of the L2 gather peak (roofline_l2)")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="assemble outputs with NCCL collectives instead of peer stores")
     args = ap.parse_args()

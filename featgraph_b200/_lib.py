@@ -26,11 +26,12 @@ class FeatGraphError(RuntimeError):
 EXPORTED_SYMBOLS = (
     "fg_last_error_string", "fg_version",
     "fg_spmm_plan_create", "fg_spmm_plan_destroy", "fg_spmm_plan_describe",
-    "fg_spmm_plan_num_launches", "fg_spmm_plan_status", "fg_spmm_csr_f32", "fg_spmm_csr_f32_host",
+    "fg_spmm_plan_num_launches", "fg_spmm_plan_status", "fg_spmm_plan_set_poll_limit", "fg_spmm_csr_f32", "fg_spmm_csr_f32_host",
     "fg_spmm_csr_f32_noalloc", "fg_spmm_noalloc_max_rows", "fg_spmm_csr_f32_multi",
     "fg_sddmm_coo_f32_multi", "fg_sddmm_coo_f32_push",
     "fg_sddmm_coo_f32", "fg_sddmm_coo_f32_host", "fg_sddmm_num_launches", "fg_sddmm_describe",
     "fg_shard_rows_by_nnz", "fg_shard_edges",
+    "fg_spmm_csr_f32_mcast", "fg_sddmm_coo_f32_mcast", "fg_peer_barrier", "fg_gather_probe",
 )
 
 
@@ -52,6 +53,7 @@ def load():
     lib.fg_spmm_plan_describe.argtypes = [c_void, ctypes.c_char_p, i64]
     lib.fg_spmm_plan_num_launches.argtypes = [c_void]
     lib.fg_spmm_plan_status.argtypes = [c_void, c_i32p]
+    lib.fg_spmm_plan_set_poll_limit.argtypes = [c_void, i64]
     lib.fg_spmm_csr_f32.argtypes = [c_void] * 7
     lib.fg_spmm_csr_f32_host.argtypes = [c_void] * 9
     lib.fg_spmm_csr_f32_multi.argtypes = [c_void] * 5 + [ctypes.POINTER(c_void), i32, c_void]
@@ -64,6 +66,11 @@ def load():
     lib.fg_sddmm_coo_f32_host.argtypes = [c_void] * 8 + [i64, i64, i64, i32, i32, i32, c_void]
     lib.fg_sddmm_num_launches.argtypes = [i64, i32, i32]
     lib.fg_sddmm_describe.argtypes = [i64, i32, i32, ctypes.c_char_p, i64]
+    lib.fg_spmm_csr_f32_mcast.argtypes = [c_void] * 7
+    lib.fg_sddmm_coo_f32_mcast.argtypes = [c_void] * 5 + [i64, i64, i64, i32, i32, i32, c_void]
+    lib.fg_peer_barrier.argtypes = [ctypes.POINTER(c_void), i32, i32, ctypes.c_uint32, c_void,
+                                    i64, i32, c_void]
+    lib.fg_gather_probe.argtypes = [c_void, i64, i32, i64, i32, c_void, i32, c_void]
     lib.fg_shard_rows_by_nnz.argtypes = [c_i32p, i64, i32, c_i64p]
     lib.fg_shard_edges.argtypes = [i64, i32, c_i64p]
     _lib = lib

@@ -13,6 +13,9 @@ parameters and print the mean of 5 runs; the kernels here have no such parameter
 JSON line per feature length is printed: mean milliseconds over ``--num-runs`` launches
 (kernel only, inputs resident, as ``measure_average_time``), GFLOP/s and algorithmic GB/s.
 Under torchrun the graph is sharded over the ranks and the all-gather is inside the time.
+The features are seeded N(0,1) arrays (``graphs.normal_features`` with FEAT_SEED for the
+array indexed by column, FEAT2_SEED for the one indexed by row); ``--dump-output FILE``
+saves the last feature length's result as a ``.npy`` file so that it can be checked.
 """
 import argparse
 import json
@@ -33,10 +36,17 @@ def _load_graph(args, device):
         m = sp.load_npz(args.dataset)
         csr = m.tocsr().astype(np.float32)
         csr.sort_indices()
-        return graphs.CSRGraph(csr.shape[0], csr.shape[1],
-                               torch.from_numpy(csr.indptr.astype(np.int32)).to(device),
-                               torch.from_numpy(csr.indices.astype(np.int32)).to(device),
-                               torch.from_numpy(csr.data).to(device)), "file:" + args.dataset
+        g = graphs.CSRGraph(csr.shape[0], csr.shape[1],
+                            torch.from_numpy(csr.indptr.astype(np.int32)).to(device),
+                            torch.from_numpy(csr.indices.astype(np.int32)).to(device),
+                            torch.from_numpy(csr.data).to(device))
+        if args.kernel == "sddmm":
+            # the edge list exactly as stored (a COO file keeps its order, as the
+            # reference's SDDMM module does: python/featgraph/module/sddmm.py:28-31, 51-52)
+            coo = m if m.format == "coo" else m.tocoo()
+            g.edge_list = (torch.from_numpy(coo.row.astype(np.int32)).to(device),
+                           torch.from_numpy(coo.col.astype(np.int32)).to(device))
+        return g, "file:" + args.dataset
     if args.synthetic == "powerlaw":
         g = graphs.powerlaw_graph(n=args.vertices or graphs.REDDIT_NUM_VERTICES,
                                   nnz_target=args.edges or graphs.REDDIT_NUM_EDGES, device=device)
@@ -66,6 +76,8 @@ def main(argv=None):
     ap.add_argument("--row-partitions", type=int, default=1,
                     help="SDDMM: the reference's 2-D edge blocking (VanillaSDDMMx86's arguments)")
     ap.add_argument("--col-partitions", type=int, default=1)
+    ap.add_argument("--dump-output", type=str, default=None,
+                    help="save the (last) result array to this .npy file (rank 0)")
     args = ap.parse_args(argv)
     if args.target != "cuda":
         raise SystemExit("this backend ships the cuda target only (no x86 code path)")
@@ -81,6 +93,7 @@ def main(argv=None):
 
     g, source = _load_graph(args, device)
     n, nnz = g.n_rows, g.nnz
+    records = []
     if args.heads > 1:
         feat_lens = [args.heads * (args.head_dim or 16)]
     else:
@@ -88,6 +101,9 @@ def main(argv=None):
     adj = g.to_scipy() if args.kernel == "spmm" else None
     rows = g.coo_rows() if args.kernel == "sddmm" else None
     cols = g.indices
+    if args.kernel == "sddmm" and hasattr(g, "edge_list"):
+        rows, cols = g.edge_list
+        nnz = int(rows.shape[0])
     if args.kernel == "sddmm" and (args.row_partitions > 1 or args.col_partitions > 1):
         # the blocked edge order of util_partition_adj_coo_2d (row partition major, column
         # partition minor, row-major inside a block), computed on the device
@@ -127,18 +143,22 @@ def main(argv=None):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         ms = float(ms)
         if rank == 0:
-            print(json.dumps({
+            if args.dump_output:
+                np.save(args.dump_output, op.out.cpu().numpy())
+            records.append({
                 "kernel": args.kernel, "graph": source, "rows": n, "nnz": nnz, "feat_len": f,
                 "heads": args.heads, "n_gpus": world, "num_runs": args.num_runs,
                 "partitions": [args.row_partitions, args.col_partitions],
                 "ms": round(ms, 4), "gflops": round(2.0 * nnz * f / ms / 1e6, 1),
                 "alg_gbs": round(alg / ms / 1e6, 1),
                 "frac_of_8TBs": round(alg / ms / 1e6 / NOMINAL_HBM_GBS, 4),
-                "degree": g.degree_stats()}), flush=True)
+                "degree": g.degree_stats()})
+            print(json.dumps(records[-1]), flush=True)
         del op, x
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return records
 
 
 if __name__ == "__main__":

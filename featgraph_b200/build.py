@@ -10,7 +10,7 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(CSRC, "libfeatgraph_b200.so")
-SOURCES = ["api.cu", "spmm.cu", "spmm_noalloc.cu", "sddmm.cu"]
+SOURCES = ["api.cu", "spmm.cu", "spmm_noalloc.cu", "sddmm.cu", "peer.cu"]
 HEADERS = ["common.cuh", os.path.join("..", "..", "include", "featgraph_b200.h")]
 
 NVCC_FLAGS = [

@@ -59,6 +59,7 @@ extern "C" int fg_shard_edges(int64_t nnz, int32_t world, int64_t* bounds) {
   if (!bounds) return fail(FG_ERR_INVALID_ARGUMENT, "null bounds");
   if (nnz < 0 || world <= 0)
     return fail(FG_ERR_INVALID_ARGUMENT, "bad nnz=%lld or world=%d", (long long)nnz, (int)world);
-  for (int32_t k = 0; k <= world; ++k) bounds[k] = (nnz * k) / world;
+  const int64_t chunk = ((nnz + world - 1) / world + 31) / 32 * 32;
+  for (int32_t k = 0; k <= world; ++k) bounds[k] = std::min<int64_t>(nnz, chunk * k);
   return FG_OK;
 }

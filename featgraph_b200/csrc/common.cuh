@@ -16,11 +16,23 @@ namespace fg {
 // Where a kernel writes its result: the caller's own buffer and, in a multi-GPU run,
 // the same position in the buffers of up to seven peers (peer-mapped pointers, plain
 // stores over NVLink) -- the "all-gather" then happens inside the kernel's epilogue.
+//
+// mcast != 0: p[0] is instead a MULTICAST address (an NVLink-switch multicast object that
+// maps the same buffer on every GPU of the group, this one included) and n == 1: one
+// multimem.st leaves the GPU once and the switch writes every GPU's copy.
 constexpr int kMaxOutputs = 8;
 struct OutPtrs {
   float* p[kMaxOutputs];
   int n;
+  int mcast;
 };
+
+// The flag arrays of fg_peer_barrier, one per rank (peer-mapped pointers), and how long a
+// wait polls by default: about a microsecond per poll, so a few seconds.
+struct PeerFlags {
+  unsigned* p[kMaxOutputs];
+};
+constexpr unsigned kPeerBarrierPolls = 1u << 22;
 
 // ---- host side: per-thread error message -----------------------------------
 std::string& last_error();
@@ -80,6 +92,34 @@ __device__ __forceinline__ float4 ld_gather4(const float* p) {
 
 __device__ __forceinline__ void st_stream4(float* p, float4 v) {
   __stcs(reinterpret_cast<float4*>(p), v);
+}
+
+// ---- result stores: every listed buffer, or one multicast store ---------------
+__device__ __forceinline__ void out_store(const OutPtrs& o, size_t off, float v) {
+  if (o.mcast) {
+    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(o.p[0] + off), "f"(v)
+                 : "memory");
+    return;
+  }
+  for (int q = 0; q < o.n; ++q) __stcs(o.p[q] + off, v);
+}
+__device__ __forceinline__ void out_store(const OutPtrs& o, size_t off, float2 v) {
+  if (o.mcast) {
+    asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(o.p[0] + off),
+                 "f"(v.x), "f"(v.y)
+                 : "memory");
+    return;
+  }
+  for (int q = 0; q < o.n; ++q) __stcs(reinterpret_cast<float2*>(o.p[q] + off), v);
+}
+__device__ __forceinline__ void out_store(const OutPtrs& o, size_t off, float4 v) {
+  if (o.mcast) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(o.p[0] + off),
+                 "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+    return;
+  }
+  for (int q = 0; q < o.n; ++q) st_stream4(o.p[q] + off, v);
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

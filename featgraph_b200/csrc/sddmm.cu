@@ -164,16 +164,14 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
       acc = mul_then_add(acc, a.z, b.z);
       acc = mul_then_add(acc, a.w, b.w);
       if (HEAD_DIM > 0 && ((q + 1) * 4) % (HEAD_DIM > 0 ? HEAD_DIM : 4) == 0) {
-        if (e < nnz)
-          for (int o = 0; o < out.n; ++o) out.p[o][(size_t)e * H + head] = acc;
+        if (e < nnz) out_store(out, (size_t)e * H + head, acc);
         ++head;
         acc = 0.f;
       }
     }
     ++chunk;
     if (HEAD_DIM == 0 && chunk % chunks_per_head == 0) {
-      if (e < nnz)
-        for (int o = 0; o < out.n; ++o) out.p[o][(size_t)e * H + head] = acc;
+      if (e < nnz) out_store(out, (size_t)e * H + head, acc);
       ++head;
       acc = 0.f;
     }
@@ -203,7 +201,7 @@ sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
   const float* d = dst + (size_t)row[e] * F + (size_t)h * D;
   float acc = 0.f;
   for (int k = 0; k < D; ++k) acc = mul_then_add(acc, s[k], d[k]);
-  for (int o = 0; o < out.n; ++o) out.p[o][i] = acc;
+  out_store(out, (size_t)i, acc);
 }
 
 constexpr int kSdTilesPerWarp = 16;
@@ -304,17 +302,17 @@ extern "C" int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_head
   return FG_OK;
 }
 
-extern "C" int fg_sddmm_coo_f32_multi(const int32_t* row, const int32_t* col, const float* src,
-                                      const float* dst, float* const* outs, int32_t n_outs,
-                                      int64_t nnz, int64_t n_rows, int64_t n_cols,
-                                      int32_t feat_len, int32_t num_heads, int32_t device,
-                                      void* stream) {
+static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src,
+                        const float* dst, float* const* outs, int32_t n_outs, int mcast,
+                        int64_t nnz, int64_t n_rows, int64_t n_cols, int32_t feat_len,
+                        int32_t num_heads, int32_t device, void* stream) {
   using namespace fg;
   if (!outs || n_outs < 1 || n_outs > kMaxOutputs)
     return fail(FG_ERR_INVALID_ARGUMENT, "need 1 to %d output pointers, got %d", kMaxOutputs,
                 (int)n_outs);
   OutPtrs out;
   out.n = n_outs;
+  out.mcast = mcast;
   for (int q = 0; q < kMaxOutputs; ++q) out.p[q] = q < n_outs ? outs[q] : nullptr;
   if (nnz < 0 || n_rows < 0 || n_cols < 0 || feat_len <= 0 || num_heads <= 0)
     return fail(FG_ERR_INVALID_ARGUMENT, "bad shape: nnz=%lld n_rows=%lld n_cols=%lld feat_len=%d heads=%d",
@@ -375,6 +373,25 @@ extern "C" int fg_sddmm_coo_f32_multi(const int32_t* row, const int32_t* col, co
   return FG_OK;
 }
 
+extern "C" int fg_sddmm_coo_f32_multi(const int32_t* row, const int32_t* col, const float* src,
+                                      const float* dst, float* const* outs, int32_t n_outs,
+                                      int64_t nnz, int64_t n_rows, int64_t n_cols,
+                                      int32_t feat_len, int32_t num_heads, int32_t device,
+                                      void* stream) {
+  return sddmm_launch(row, col, src, dst, outs, n_outs, 0, nnz, n_rows, n_cols, feat_len,
+                      num_heads, device, stream);
+}
+
+extern "C" int fg_sddmm_coo_f32_mcast(const int32_t* row, const int32_t* col, const float* src,
+                                      const float* dst, float* out_mcast, int64_t nnz,
+                                      int64_t n_rows, int64_t n_cols, int32_t feat_len,
+                                      int32_t num_heads, int32_t device, void* stream) {
+  if (nnz > 0 && !out_mcast) return fg::fail(FG_ERR_INVALID_ARGUMENT, "null device pointer");
+  float* outs[1] = {out_mcast};
+  return sddmm_launch(row, col, src, dst, outs, 1, 1, nnz, n_rows, n_cols, feat_len, num_heads,
+                      device, stream);
+}
+
 extern "C" int fg_sddmm_coo_f32(const int32_t* row, const int32_t* col, const float* src,
                                 const float* dst, float* out, int64_t nnz, int64_t n_rows,
                                 int64_t n_cols, int32_t feat_len, int32_t num_heads,
@@ -408,16 +425,12 @@ extern "C" int fg_sddmm_coo_f32_host(const int32_t* row, const int32_t* col,
   // The output (4 bytes per edge and head) dominates the transfers, so the edge list is
   // cut into pieces: while piece k+1 is computed, piece k travels to the host on a second
   // stream.  Small inputs take one piece.
-  const int pieces = nnz >= (1 << 22) ? 8 : 1;
-  cudaStream_t copy_st = nullptr;
-  cudaEvent_t done[8] = {nullptr};
+  const int pieces = nnz >= (1 << 22) ? kPushMaxPieces : 1;
+  // the second stream and its events are made once per device and host thread, and kept
+  PushContext* pc = pieces > 1 ? push_context(device) : nullptr;
+  if (pieces > 1 && !pc) return fail(FG_ERR_CUDA, "cannot create the copy stream or its events");
   int rc = FG_OK;
   cudaError_t err = cudaSuccess;
-  if (pieces > 1) {
-    err = cudaStreamCreateWithFlags(&copy_st, cudaStreamNonBlocking);
-    for (int k = 0; k < pieces && err == cudaSuccess; ++k)
-      err = cudaEventCreateWithFlags(&done[k], cudaEventDisableTiming);
-  }
   for (int k = 0; k < pieces && rc == FG_OK && err == cudaSuccess; ++k) {
     const int64_t e0 = nnz * k / pieces, e1 = nnz * (k + 1) / pieces;
     if (e1 == e0) continue;
@@ -425,24 +438,21 @@ extern "C" int fg_sddmm_coo_f32_host(const int32_t* row, const int32_t* col,
                           e1 - e0, n_rows, n_cols, feat_len, num_heads, device, stream);
     if (rc != FG_OK) break;
     const size_t bytes = sizeof(float) * (size_t)(e1 - e0) * num_heads;
-    if (pieces > 1) {
-      err = cudaEventRecord(done[k], st);
-      if (err == cudaSuccess) err = cudaStreamWaitEvent(copy_st, done[k], 0);
+    if (pc) {
+      err = cudaEventRecord(pc->computed[k], st);
+      if (err == cudaSuccess) err = cudaStreamWaitEvent(pc->stream, pc->computed[k], 0);
       if (err == cudaSuccess)
         err = cudaMemcpyAsync(out_host + e0 * num_heads, out_stage + e0 * num_heads, bytes,
-                              cudaMemcpyDeviceToHost, copy_st);
+                              cudaMemcpyDeviceToHost, pc->stream);
     } else {
       err = cudaMemcpyAsync(out_host + e0 * num_heads, out_stage + e0 * num_heads, bytes,
                             cudaMemcpyDeviceToHost, st);
     }
   }
-  if (err == cudaSuccess) err = cudaStreamSynchronize(st);
-  if (copy_st) {
-    if (err == cudaSuccess) err = cudaStreamSynchronize(copy_st);
-    for (int k = 0; k < pieces; ++k)
-      if (done[k]) cudaEventDestroy(done[k]);
-    cudaStreamDestroy(copy_st);
-  }
+  // both streams are drained also after a failure: no copy of this call outlives it
+  const cudaError_t e1 = cudaStreamSynchronize(st);
+  const cudaError_t e2 = pc ? cudaStreamSynchronize(pc->stream) : cudaSuccess;
+  if (err == cudaSuccess) err = e1 != cudaSuccess ? e1 : e2;
   if (rc != FG_OK) return rc;
   if (err != cudaSuccess)
     return fail(FG_ERR_CUDA, "fg_sddmm_coo_f32_host: %s", cudaGetErrorString(err));
@@ -464,6 +474,7 @@ extern "C" int fg_sddmm_coo_f32_push(const int32_t* row, const int32_t* col, con
   if (!out) return fail(FG_ERR_INVALID_ARGUMENT, "null device pointer");
   OutPtrs peers;
   peers.n = n_peers;
+  peers.mcast = 0;
   bool vec = reinterpret_cast<uintptr_t>(out) % 16 == 0;
   for (int q = 0; q < kMaxOutputs; ++q) {
     peers.p[q] = q < n_peers ? peer_outs[q] : nullptr;

@@ -114,9 +114,7 @@ spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     if (cnt > 0) e += (cnt < G ? cnt : G);
   }
   if (valid)
-    for (int q = 0; q < Y.n; ++q)
-      st_stream4(Y.p[q] + (size_t)row * F + col_off,
-                 make_float4(acc_lo.x, acc_lo.y, acc_hi.x, acc_hi.y));
+    out_store(Y, (size_t)row * F + col_off, make_float4(acc_lo.x, acc_lo.y, acc_hi.x, acc_hi.y));
 }
 
 constexpr int kHvEdges = 32;    // nonzeros per stage
@@ -167,13 +165,10 @@ __device__ __forceinline__ void heavy_consume_stage(const float (*xt)[32 * VEC],
 template <int VEC>
 __device__ __forceinline__ void heavy_store_row(const OutPtrs& Y, size_t slab_off, int lane,
                                                 float acc_a, float acc_b) {
-  for (int q = 0; q < Y.n; ++q) {
-    float* yslab = Y.p[q] + slab_off;
-    if (VEC == 2)
-      __stcs(reinterpret_cast<float2*>(yslab + lane * 2), make_float2(acc_a, acc_b));
-    else
-      __stcs(yslab + lane, acc_a);
-  }
+  if (VEC == 2)
+    out_store(Y, slab_off + lane * 2, make_float2(acc_a, acc_b));
+  else
+    out_store(Y, slab_off + lane, acc_a);
 }
 
 // Decodes blockIdx.x of the heavy / giant kernels: items are ordered
@@ -323,12 +318,13 @@ __device__ __forceinline__ int giant_swizzle(int f) { return ((f >> 2) ^ f) & 7;
 // loads alternating with adds in one basic block; it checks a whole group's flags at
 // once and hands a group back when its last block sits in registers.  Result: 5.5
 // cycles per nonzero (14.3 with row-major segments and per-block mbarriers).
-// Every wait is a bounded poll; a wait that gives up is recorded in *status.
+// Every wait is a bounded poll (max_polls); a wait that gives up is recorded in *status
+// (the first code sticks) and the row's slab is then filled with NaN.
 __global__ void __launch_bounds__(32 * kGtWarps)
 spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
                   OutPtrs Y, const int* __restrict__ rows, int n_listed,
-                  int subs_per_slab, int F, int* __restrict__ status) {
+                  int subs_per_slab, int F, int* __restrict__ status, unsigned max_polls) {
   constexpr unsigned kFull = 0xffffffffu;
   extern __shared__ __align__(16) unsigned char giant_smem[];
   // prod[block][feature][nonzero]: a feature's 32 products of a block are 8 quads of 4
@@ -409,7 +405,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
           int got = 0;
           if (lane == 0) {
             const unsigned need = (unsigned)(grp - kGtGroups + 1);
-            for (unsigned i = 0; i < kGtMaxPolls && !got; ++i) {
+            for (unsigned i = 0; i < max_polls && !got; ++i) {
               got = ld_acquire_shared(consumed) >= need;
               if (!got) __nanosleep(64);
             }
@@ -472,7 +468,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
       if (u + 1 < my_blocks && ok) emit(u + 1, vsb, xb);
       if (u + 2 < my_blocks && ok) emit(u + 2, vsc, xc);
     }
-    if (!ok && lane == 0) atomicExch(status, kGtErrProducerTimeout);
+    if (!ok && lane == 0) atomicCAS(status, 0, kGtErrProducerTimeout);
     return;
   }
 
@@ -491,7 +487,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     const unsigned want = (unsigned)j + 1u;
     if (seen != want && !gave_up) {  // rare: the producers are behind (once given up, no more waits)
       bool got = false;
-      for (unsigned i = 0; i < kGtMaxPolls && !got; ++i) got = peek(j) == want;
+      for (unsigned i = 0; i < max_polls && !got; ++i) got = peek(j) == want;
       gave_up |= !got;
     }
     fence_acquire_cta();
@@ -601,8 +597,11 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     for (int e = 0; e < cnt; ++e) acc = __fadd_rn(acc, src[(((e >> 2) ^ swz) << 2) | (e & 3)]);
   }
   if (__any_sync(kFull, gave_up)) {
-    if (lane == 0) atomicExch(status, kGtErrConsumerTimeout);
-    return;  // the row is not written; the host sees the status
+    // No sum to report: the slab is filled with NaN so that a stale value of an earlier
+    // call cannot pass for a result, and the host finds the code in the status word.
+    if (lane == 0) atomicCAS(status, 0, kGtErrConsumerTimeout);
+    heavy_store_row<1>(Y, (size_t)row * F + (size_t)sub * 32, lane, __int_as_float(0x7fc00000), 0.f);
+    return;
   }
   heavy_store_row<1>(Y, (size_t)row * F + (size_t)sub * 32, lane, acc, 0.f);
 }
@@ -622,7 +621,7 @@ spmm_generic_kernel(const int* __restrict__ indptr, const int* __restrict__ indi
     if (f < F) {
       for (int e = beg; e < end; ++e)
         acc = mul_then_add(acc, vals[e], X[(size_t)indices[e] * F + f]);
-      for (int q = 0; q < Y.n; ++q) Y.p[q][(size_t)row * F + f] = acc;
+      out_store(Y, (size_t)row * F + f, acc);
     }
   }
 }
@@ -643,7 +642,8 @@ struct fg_spmm_plan {
   int n_giant = 0, n_heavy = 0, n_light = 0;
   int64_t max_deg = 0, giant_nnz = 0, heavy_nnz = 0;
   int* rows_dev = nullptr;    // the whole sorted list
-  int* status_dev = nullptr;  // set by a giant-kernel barrier wait that gave up
+  int* status_dev = nullptr;  // set by a giant-kernel wait that gave up
+  unsigned poll_limit = 0;    // polls a giant-kernel wait makes before it gives up
   cudaStream_t aux_giant = nullptr, aux_heavy = nullptr;
   cudaEvent_t fork_ev = nullptr, join_giant = nullptr, join_heavy = nullptr;
   int l2_bytes = 0, n_sms = 0;
@@ -687,10 +687,44 @@ static int choose_slab_width(int F, int64_t n_cols, int l2_bytes) {
 
 }  // namespace fg
 
-extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols,
-                                   int32_t feat_len, int32_t device, int32_t heavy_threshold,
-                                   fg_spmm_plan** out_plan) {
-  using namespace fg;
+namespace fg {
+
+// Rows by degree, descending, ties in row order (a stable sort): the hardware block
+// scheduler then hands out the longest rows first, and the groups that share a warp get
+// rows of (nearly) equal length.  A counting sort over the degrees below kSortCap (the
+// table stays at 16 MiB whatever the longest row is); the few rows at or over the cap are
+// sorted by comparison.
+constexpr int64_t kSortCap = 1 << 22;
+static void rows_by_degree(const int32_t* indptr, int64_t n_rows, int64_t max_deg,
+                           std::vector<int32_t>& order) {
+  auto deg = [&](int64_t r) { return (int64_t)indptr[r + 1] - indptr[r]; };
+  order.resize((size_t)n_rows);
+  const int64_t buckets = std::min<int64_t>(max_deg, kSortCap - 1) + 1;  // degrees 0 .. buckets-1
+  std::vector<int32_t> longest;
+  std::vector<int64_t> start((size_t)buckets + 1, 0);
+  for (int64_t r = 0; r < n_rows; ++r) {
+    const int64_t d = deg(r);
+    if (d >= buckets) longest.push_back((int32_t)r);
+    else start[(size_t)d]++;
+  }
+  std::stable_sort(longest.begin(), longest.end(),
+                   [&](int32_t a, int32_t b) { return deg(a) > deg(b); });
+  std::copy(longest.begin(), longest.end(), order.begin());
+  // start[d] <- position of the first row of degree d
+  int64_t running = (int64_t)longest.size();
+  for (int64_t d = buckets - 1; d >= 0; --d) {
+    const int64_t c = start[(size_t)d];
+    start[(size_t)d] = running;
+    running += c;
+  }
+  for (int64_t r = 0; r < n_rows; ++r) {
+    const int64_t d = deg(r);
+    if (d < buckets) order[(size_t)start[(size_t)d]++] = (int32_t)r;
+  }
+}
+
+static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, int32_t feat_len,
+                       int32_t device, int32_t heavy_threshold, fg_spmm_plan** out_plan) {
   if (!out_plan) return fail(FG_ERR_INVALID_ARGUMENT, "out_plan is null");
   *out_plan = nullptr;
   if (n_rows < 0 || n_cols < 0 || feat_len <= 0)
@@ -717,6 +751,7 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
   p->max_deg = max_deg;
   p->heavy_threshold = heavy_threshold > 0 ? heavy_threshold : kDefaultHeavyThreshold;
   p->vector_ok = (feat_len % 32 == 0);
+  p->poll_limit = kGtMaxPolls;
 
   DeviceGuard guard(device);
   if (guard.status != cudaSuccess) {
@@ -767,34 +802,30 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
   }
 
   if (p->vector_ok && n_rows > 0) {
-    // Stable counting sort of the rows by degree, descending: the hardware
-    // block scheduler then hands out the longest rows first, and the groups
-    // that share a warp get rows of (nearly) equal length.
-    std::vector<int32_t> start((size_t)max_deg + 2, 0);
-    for (int64_t r = 0; r < n_rows; ++r) start[(size_t)(indptr[r + 1] - indptr[r])]++;
-    // start[d] <- number of rows with degree > d
-    int64_t running = 0;
-    for (int64_t d = max_deg; d >= 0; --d) {
-      const int32_t c = start[(size_t)d];
-      start[(size_t)d] = (int32_t)running;
-      running += c;
+    std::vector<int32_t> order;
+    try {
+      rows_by_degree(indptr, n_rows, max_deg, order);
+    } catch (const std::bad_alloc&) {
+      plan_release(p);
+      return fail(FG_ERR_OUT_OF_MEMORY, "fg_spmm_plan_create: host allocation failed");
     }
-    std::vector<int32_t> order((size_t)n_rows);
-    for (int64_t r = 0; r < n_rows; ++r)
-      order[(size_t)start[(size_t)(indptr[r + 1] - indptr[r])]++] = (int32_t)r;
     auto degree_at = [&](int64_t k) {
       return (int64_t)indptr[order[(size_t)k] + 1] - indptr[order[(size_t)k]];
     };
-    // Giant class: rows over the giant threshold, but no more (row, slab) CTAs
-    // than SMs -- a giant CTA wants an SM's worth of copy bandwidth to itself.
-    // and no more giant CTAs (row, 32-float slab) than fit a 32-bit grid
-    const int64_t giant_cap = (int64_t)INT32_MAX / std::max(1, feat_len / 32);
+    // Giant class: the rows over the giant threshold, as long as their (row, 32-float
+    // slab) CTAs fit a 32-bit grid; likewise the heavy class and the light items.
+    const int64_t grid_cap = (int64_t)INT32_MAX / std::max(1, feat_len / 32);
     int64_t k = 0;
-    while (k < n_rows && k < giant_cap && degree_at(k) > p->giant_threshold) p->giant_nnz += degree_at(k++);
+    while (k < n_rows && k < grid_cap && degree_at(k) > p->giant_threshold) p->giant_nnz += degree_at(k++);
     p->n_giant = (int)k;
     while (k < n_rows && degree_at(k) > p->heavy_threshold) p->heavy_nnz += degree_at(k++);
     p->n_heavy = (int)(k - p->n_giant);
     p->n_light = (int)(n_rows - k);
+    if ((int64_t)p->n_heavy * (feat_len / 32) >= INT32_MAX ||
+        (int64_t)p->n_light * (feat_len / 32) >= INT32_MAX) {
+      plan_release(p);
+      return fail(FG_ERR_UNSUPPORTED, "too many (row, slab) items for one launch");
+    }
 
     FG_PLAN_TRY(cudaMalloc(&p->rows_dev, sizeof(int32_t) * (size_t)n_rows));
     FG_PLAN_TRY(cudaMemcpy(p->rows_dev, order.data(), sizeof(int32_t) * (size_t)n_rows,
@@ -829,6 +860,21 @@ extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_
   return FG_OK;
 }
 
+}  // namespace fg
+
+extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols,
+                                   int32_t feat_len, int32_t device, int32_t heavy_threshold,
+                                   fg_spmm_plan** out_plan) {
+  // the host-side containers may throw; the C ABI never does
+  try {
+    return fg::plan_create(indptr, n_rows, n_cols, feat_len, device, heavy_threshold, out_plan);
+  } catch (const std::bad_alloc&) {
+    return fg::fail(FG_ERR_OUT_OF_MEMORY, "fg_spmm_plan_create: host allocation failed");
+  } catch (...) {
+    return fg::fail(FG_ERR_CUDA, "fg_spmm_plan_create: unexpected exception");
+  }
+}
+
 extern "C" int fg_spmm_plan_destroy(fg_spmm_plan* plan) {
   fg::plan_release(plan);
   return FG_OK;
@@ -844,9 +890,20 @@ extern "C" int fg_spmm_plan_status(const fg_spmm_plan* p, int32_t* device_status
   int v = 0;
   FG_CUDA_TRY(cudaMemcpy(&v, p->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
   *device_status = v;
-  if (v != 0)
-    return fail(FG_ERR_CUDA, "spmm_giant_kernel: a bounded barrier wait gave up (code %d: %s warp)",
-                v, v == kGtErrProducerTimeout ? "producer" : "consumer");
+  if (v != 0) {
+    // reported once: the word is cleared so that later calls are judged on their own
+    FG_CUDA_TRY(cudaMemset(p->status_dev, 0, sizeof(int)));
+    return fail(FG_ERR_CUDA, "spmm_giant_kernel: a bounded wait gave up (code %d: %s warp); "
+                "the rows it was summing hold NaN", v,
+                v == kGtErrProducerTimeout ? "producer" : "consumer");
+  }
+  return FG_OK;
+}
+
+extern "C" int fg_spmm_plan_set_poll_limit(fg_spmm_plan* p, int64_t polls) {
+  using namespace fg;
+  if (!p) return fail(FG_ERR_INVALID_ARGUMENT, "plan is null");
+  p->poll_limit = polls < 0 ? kGtMaxPolls : (unsigned)std::min<int64_t>(polls, kGtMaxPolls);
   return FG_OK;
 }
 
@@ -902,9 +959,9 @@ static void launch_light(const fg_spmm_plan* p, const int32_t* indptr, const int
 
 }  // namespace fg
 
-extern "C" int fg_spmm_csr_f32_multi(const fg_spmm_plan* p, const int32_t* indptr,
-                                     const int32_t* indices, const float* vals, const float* x,
-                                     float* const* ys, int32_t n_ys, void* stream) {
+static int spmm_launch(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
+                       const float* vals, const float* x, float* const* ys, int32_t n_ys,
+                       int mcast, void* stream) {
   using namespace fg;
   if (!p) return fail(FG_ERR_INVALID_ARGUMENT, "plan is null");
   if (!ys || n_ys < 1 || n_ys > kMaxOutputs)
@@ -913,6 +970,7 @@ extern "C" int fg_spmm_csr_f32_multi(const fg_spmm_plan* p, const int32_t* indpt
   if (p->n_rows == 0) return FG_OK;
   OutPtrs y;
   y.n = n_ys;
+  y.mcast = mcast;
   bool aligned = reinterpret_cast<uintptr_t>(x) % 16 == 0;
   for (int q = 0; q < kMaxOutputs; ++q) {
     y.p[q] = q < n_ys ? ys[q] : nullptr;
@@ -938,46 +996,77 @@ extern "C" int fg_spmm_csr_f32_multi(const fg_spmm_plan* p, const int32_t* indpt
 
   // Fork: giant and heavy rows run on the plan's own high-priority streams, the
   // longest first, while the light kernel fills the rest of the machine; the
-  // caller's stream joins both before the call returns control to it.
+  // caller's stream joins both before the call returns control to it -- also when a
+  // later launch fails, so that no kernel of this call is left writing Y unobserved.
   const int slab = 32 * p->heavy_vec;
   const int hv_slabs = p->feat_len / slab;
   if (p->fork_ev) FG_CUDA_TRY(cudaEventRecord(p->fork_ev, st));
-  if (p->n_giant > 0) {
-    FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_giant, p->fork_ev, 0));
-    // one CTA per (row, 32-float slab), whatever the heavy kernel's slab is
-    const unsigned grid = (unsigned)(p->n_giant * (p->feat_len / 32));
-    spmm_giant_kernel<<<grid, 32 * kGtWarps, kGtSmemBytes, p->aux_giant>>>(
-        indptr, indices, vals, x, y, p->rows_dev, p->n_giant, p->slab_w / 32, p->feat_len,
-        p->status_dev);
-    FG_CUDA_TRY(cudaGetLastError());
-    FG_CUDA_TRY(cudaEventRecord(p->join_giant, p->aux_giant));
-  }
-  if (p->n_heavy > 0) {
-    FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_heavy, p->fork_ev, 0));
-    const long long items = (long long)p->n_heavy * hv_slabs;
-    if (items >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "too many heavy items");
-    if (p->heavy_vec == 2)
-      spmm_heavy_kernel<2><<<(unsigned)items, 32, heavy_smem_bytes<2>(), p->aux_heavy>>>(
-          indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
-          p->feat_len);
-    else
-      spmm_heavy_kernel<1><<<(unsigned)items, 32, heavy_smem_bytes<1>(), p->aux_heavy>>>(
-          indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
-          p->feat_len);
-    FG_CUDA_TRY(cudaGetLastError());
-    FG_CUDA_TRY(cudaEventRecord(p->join_heavy, p->aux_heavy));
-  }
-  if (p->n_light > 0) {
-    switch (p->slab_w) {
-      case 128: launch_light<32>(p, indptr, indices, vals, x, y, st); break;
-      case 64: launch_light<16>(p, indptr, indices, vals, x, y, st); break;
-      default: launch_light<8>(p, indptr, indices, vals, x, y, st); break;
+  bool giant_forked = false, heavy_forked = false;
+  auto launch_all = [&]() -> int {
+    if (p->n_giant > 0) {
+      FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_giant, p->fork_ev, 0));
+      // one CTA per (row, 32-float slab), whatever the heavy kernel's slab is
+      const unsigned grid = (unsigned)(p->n_giant * (p->feat_len / 32));
+      spmm_giant_kernel<<<grid, 32 * kGtWarps, kGtSmemBytes, p->aux_giant>>>(
+          indptr, indices, vals, x, y, p->rows_dev, p->n_giant, p->slab_w / 32, p->feat_len,
+          p->status_dev, p->poll_limit);
+      giant_forked = true;
+      FG_CUDA_TRY(cudaGetLastError());
     }
-    FG_CUDA_TRY(cudaGetLastError());
+    if (p->n_heavy > 0) {
+      FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_heavy, p->fork_ev, 0));
+      const long long items = (long long)p->n_heavy * hv_slabs;  // < INT32_MAX: checked by the plan
+      if (p->heavy_vec == 2)
+        spmm_heavy_kernel<2><<<(unsigned)items, 32, heavy_smem_bytes<2>(), p->aux_heavy>>>(
+            indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
+            p->feat_len);
+      else
+        spmm_heavy_kernel<1><<<(unsigned)items, 32, heavy_smem_bytes<1>(), p->aux_heavy>>>(
+            indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
+            p->feat_len);
+      heavy_forked = true;
+      FG_CUDA_TRY(cudaGetLastError());
+    }
+    if (p->n_light > 0) {
+      switch (p->slab_w) {
+        case 128: launch_light<32>(p, indptr, indices, vals, x, y, st); break;
+        case 64: launch_light<16>(p, indptr, indices, vals, x, y, st); break;
+        default: launch_light<8>(p, indptr, indices, vals, x, y, st); break;
+      }
+      FG_CUDA_TRY(cudaGetLastError());
+    }
+    return FG_OK;
+  };
+  const int rc = launch_all();
+  cudaError_t join_err = cudaSuccess;
+  if (giant_forked) {
+    join_err = cudaEventRecord(p->join_giant, p->aux_giant);
+    if (join_err == cudaSuccess) join_err = cudaStreamWaitEvent(st, p->join_giant, 0);
   }
-  if (p->n_giant > 0) FG_CUDA_TRY(cudaStreamWaitEvent(st, p->join_giant, 0));
-  if (p->n_heavy > 0) FG_CUDA_TRY(cudaStreamWaitEvent(st, p->join_heavy, 0));
+  if (heavy_forked) {
+    cudaError_t e = cudaEventRecord(p->join_heavy, p->aux_heavy);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(st, p->join_heavy, 0);
+    if (join_err == cudaSuccess) join_err = e;
+  }
+  if (rc != FG_OK) return rc;
+  if (join_err != cudaSuccess)
+    return fail(FG_ERR_CUDA, "joining the plan's streams failed: %s", cudaGetErrorString(join_err));
   return FG_OK;
+}
+
+extern "C" int fg_spmm_csr_f32_multi(const fg_spmm_plan* p, const int32_t* indptr,
+                                     const int32_t* indices, const float* vals, const float* x,
+                                     float* const* ys, int32_t n_ys, void* stream) {
+  return spmm_launch(p, indptr, indices, vals, x, ys, n_ys, 0, stream);
+}
+
+extern "C" int fg_spmm_csr_f32_mcast(const fg_spmm_plan* p, const int32_t* indptr,
+                                     const int32_t* indices, const float* vals, const float* x,
+                                     float* y_mcast, void* stream) {
+  if (p && p->n_rows > 0 && !y_mcast)
+    return fg::fail(FG_ERR_INVALID_ARGUMENT, "y_mcast_dev is null");
+  float* ys[1] = {y_mcast};
+  return spmm_launch(p, indptr, indices, vals, x, ys, 1, 1, stream);
 }
 
 extern "C" int fg_spmm_csr_f32(const fg_spmm_plan* p, const int32_t* indptr,

@@ -114,9 +114,26 @@ class SDDMMbase(object):
         stores 0.67 ms per SDDMM, push 1.01 ms; on 2 GPUs 1.49 against 1.78 ms."""
         self._extra_outputs = [int(p) for p in device_pointers]
         self._push_outputs = bool(push)
+        self._mcast_output = None
+
+    def set_multicast_output(self, mcast_pointer):
+        """Deliver every result with ONE store to this address instead: the position of the
+        edge range inside an NVLink-switch multicast mapping of the output, which the switch
+        writes into every GPU's copy (this GPU's included).  None switches it off."""
+        self._mcast_output = int(mcast_pointer) if mcast_pointer else None
+        self._extra_outputs = None
 
     def _launch(self, src, dst):
         a = self._spec.attrs
+        mcast = getattr(self, "_mcast_output", None)
+        if mcast:
+            import ctypes
+            _lib.check(_lib.load().fg_sddmm_coo_f32_mcast(
+                ptr(self._adj_row_indices_tvm.torch), ptr(self._adj_col_indices_tvm.torch),
+                ptr(src), ptr(dst), ctypes.c_void_p(mcast), self._adj_row_indices.shape[0],
+                self._num_rows, self._num_cols, a["feat_len"], a["num_heads"],
+                self._ctx.device_id, current_stream_handle(self._ctx)))
+            return
         extra = getattr(self, "_extra_outputs", None)
         if extra and getattr(self, "_push_outputs", False):
             import ctypes

@@ -136,8 +136,23 @@ class SpMMbase(object):
         """Also store every result row at these device addresses (peer-mapped copies of the
         output block on other GPUs, at most 7): the multi-GPU path's fused all-gather."""
         self._extra_outputs = [int(p) for p in device_pointers]
+        self._mcast_output = None
+
+    def set_multicast_output(self, mcast_pointer):
+        """Store every result row ONCE to this address instead: the position of the row block
+        inside an NVLink-switch multicast mapping of the output, which the switch writes into
+        every GPU's copy (this GPU's included).  None switches it off."""
+        self._mcast_output = int(mcast_pointer) if mcast_pointer else None
+        self._extra_outputs = None
 
     def _launch(self, x):
+        mcast = getattr(self, "_mcast_output", None)
+        if mcast:
+            _lib.check(_lib.load().fg_spmm_csr_f32_mcast(
+                self._plan, ptr(self._adj_indptr_tvm.torch), ptr(self._adj_indices_tvm.torch),
+                ptr(self._adj_vals_tvm.torch), ptr(x), ctypes.c_void_p(mcast),
+                current_stream_handle(self._ctx)))
+            return
         extra = getattr(self, "_extra_outputs", None)
         if extra:
             outs = (ctypes.c_void_p * (1 + len(extra)))(self.out_tvm.torch.data_ptr(), *extra)
@@ -193,9 +208,15 @@ class SpMMbase(object):
             ptr(self.out_tvm.torch), current_stream_handle(self._ctx)))
         return y_host
 
+    def set_poll_limit(self, polls):
+        """Test hook: how often a wait inside the giant-row kernel polls before it gives up
+        (negative: the default)."""
+        _lib.check(_lib.load().fg_spmm_plan_set_poll_limit(self._plan, int(polls)))
+
     def device_status(self):
         """Synchronise and return the status word of the plan's kernels: 0 when every
-        bounded device-side wait completed; raises FeatGraphError otherwise."""
+        bounded device-side wait completed; raises FeatGraphError otherwise (once: the
+        word is cleared when it is reported)."""
         if self._plan is None:
             return 0
         status = ctypes.c_int32(0)

@@ -37,10 +37,14 @@ const char* fg_version(void);
 
 /* ------------------------------------------------------------------ SpMM -- */
 
-/* Opaque launch plan of one CSR matrix: rows binned by degree (a light list
- * served by sub-warp groups, a heavy list served by staged single-warp CTAs),
- * the feature-slab width chosen from the device's L2 size, an auxiliary
- * stream and two events used to overlap the heavy and the light kernel. */
+/* Opaque launch plan of one CSR matrix: the rows sorted by degree and cut into
+ * three classes (light rows served by sub-warp groups, heavy rows by staged
+ * single-warp CTAs, the few giant rows by producer/consumer CTAs), the
+ * feature-slab width chosen from the device's L2 size, and two auxiliary
+ * streams with their fork/join events on which the heavy and the giant kernel
+ * run beside the light one.  Those streams and events are shared by every call
+ * that uses the plan: one call in flight per plan (calls on one stream are
+ * fine; two host threads or two streams using one plan at once race). */
 typedef struct fg_spmm_plan fg_spmm_plan;
 
 /* Builds the plan from the HOST copy of indptr (n_rows + 1 int32 entries).
@@ -60,10 +64,20 @@ int fg_spmm_plan_destroy(fg_spmm_plan* plan);
 int fg_spmm_plan_describe(const fg_spmm_plan* plan, char* buf, int64_t buf_len);
 
 /* Synchronises the plan's device and reads the status word its kernels write:
- * 0 = fine; non-zero = a bounded wait inside the heavy-row kernel gave up (the
- * call then also returns FG_ERR_CUDA and the affected rows were not written).
- * The reference has no counterpart (TVM kernels have no device-side waits). */
+ * 0 = fine; non-zero = a bounded wait inside the giant-row kernel gave up since
+ * the last time this function was called (1: a producer warp, 2: the consumer
+ * warp).  In that case this function also returns FG_ERR_CUDA, the rows that
+ * kernel was summing hold NaN in Y, and the word is cleared, so the next SpMM
+ * call is judged on its own.  The reference has no counterpart (TVM kernels
+ * have no device-side waits). */
 int fg_spmm_plan_status(const fg_spmm_plan* plan, int32_t* device_status);
+
+/* Sets how many times a wait inside the giant-row kernel polls before it gives
+ * up (default 2^20; polls < 0 restores the default; 0 = never wait).  A hook
+ * for tests of the give-up path: with a tiny limit the kernel still returns,
+ * reports through fg_spmm_plan_status and fills the affected rows with NaN.
+ * No counterpart in the reference. */
+int fg_spmm_plan_set_poll_limit(fg_spmm_plan* plan, int64_t polls);
 
 /* Number of kernels one fg_spmm_csr_f32 call launches with this plan. */
 int fg_spmm_plan_num_launches(const fg_spmm_plan* plan);
@@ -90,6 +104,17 @@ int fg_spmm_csr_f32_multi(const fg_spmm_plan* plan, const int32_t* indptr_dev,
                           const int32_t* indices_dev, const float* vals_dev,
                           const float* x_dev, float* const* ys_host_array, int32_t n_ys,
                           void* stream);
+
+/* The same SpMM with every finished row stored ONCE through an NVLink-switch
+ * multicast address: y_mcast_dev is the position of this call's first row inside
+ * a multicast mapping of an output buffer that every GPU of the group holds (e.g.
+ * torch symmetric memory's multicast_ptr); the switch writes the row into every
+ * GPU's copy, this GPU's included (multimem.st; a store, never a multicast load).
+ * The caller still has to synchronise the GPUs before anyone reads (fg_peer_barrier).
+ * No counterpart in the reference (single device, python/featgraph/module/spmm.py:218). */
+int fg_spmm_csr_f32_mcast(const fg_spmm_plan* plan, const int32_t* indptr_dev,
+                          const int32_t* indices_dev, const float* vals_dev,
+                          const float* x_dev, float* y_mcast_dev, void* stream);
 
 /* Same computation from HOST buffers: uploads X, launches, downloads Y and
  * synchronises the stream.  The adjacency stays resident on the device, as it
@@ -152,6 +177,15 @@ int fg_sddmm_coo_f32_multi(const int32_t* row_dev, const int32_t* col_dev,
                            int64_t n_rows, int64_t n_cols, int32_t feat_len,
                            int32_t num_heads, int32_t device, void* stream);
 
+/* The same SDDMM with every result stored once through an NVLink-switch multicast
+ * address (see fg_spmm_csr_f32_mcast): out_mcast_dev is the position of this call's
+ * first edge inside the multicast mapping of the output.  No counterpart in the
+ * reference. */
+int fg_sddmm_coo_f32_mcast(const int32_t* row_dev, const int32_t* col_dev,
+                           const float* src_dev, const float* dst_dev, float* out_mcast_dev,
+                           int64_t nnz, int64_t n_rows, int64_t n_cols, int32_t feat_len,
+                           int32_t num_heads, int32_t device, void* stream);
+
 /* SDDMM of this GPU's edge range with the result also delivered to peers (multi-GPU; no
  * counterpart in the reference, which is single-device: module/sddmm.py:185).  The edge
  * list is cut into pieces; piece k is copied into the same position of every peer's
@@ -192,10 +226,41 @@ int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_heads,
 int fg_shard_rows_by_nnz(const int32_t* indptr_host, int64_t n_rows,
                          int32_t world, int64_t* bounds);
 
-/* Splits nnz edges into `world` contiguous, near-equal ranges (world + 1
- * bounds).  Pure host code; no counterpart in the reference
- * (python/featgraph/module/sddmm.py:185 is single-device). */
+/* Splits nnz edges into `world` contiguous ranges of equal length, the length
+ * rounded up to a multiple of 32 edges (so every range starts on a 128-byte
+ * boundary of a float output and one even all-gather assembles the padded
+ * result); trailing ranges may be short or empty.  bounds receives world + 1
+ * edge indices, bounds[world] = nnz.  Pure host code; no counterpart in the
+ * reference (python/featgraph/module/sddmm.py:185 is single-device). */
 int fg_shard_edges(int64_t nnz, int32_t world, int64_t* bounds);
+
+/* Device-side barrier between the `world` (at most 8) GPUs of one box, enqueued on
+ * `stream`: flag_arrays_host_array[r] is rank r's array of `world` 32-bit counters
+ * as THIS rank addresses it (peer-mapped; all zero before the first barrier), `epoch`
+ * counts the barriers (1, 2, 3, ... on every rank alike).  The kernel announces the
+ * epoch in this rank's slot of every array and waits, at most max_polls polls per
+ * peer (about a microsecond each; < 0 selects the default, a few seconds), until
+ * every peer has announced it.  A wait that runs out writes 1 + the missing rank to
+ * *status_dev (an int32 the caller zeroed; the first code sticks) and the kernel
+ * returns -- nothing hangs, the host reads the word when it next synchronises.
+ * Brackets the multi-GPU calls whose kernels store into peers' outputs.  No
+ * counterpart in the reference (single device). */
+int fg_peer_barrier(uint32_t* const* flag_arrays_host_array, int32_t rank, int32_t world,
+                    uint32_t epoch, int32_t* status_dev, int64_t max_polls, int32_t device,
+                    void* stream);
+
+/* ------------------------------------------------------------ measurement -- */
+
+/* Launches a gather-only kernel: n_blocks CTAs of 256 threads, groups of
+ * row_floats / 4 lanes (row_floats = 32, 64 or 128) each read rows_per_group
+ * whole rows of table_dev (n_rows x row_floats fp32) at pseudo-random row
+ * indices, eight 16-byte loads in flight per lane.  Timed by the caller, it gives
+ * the rate at which the L2 -> SM path delivers gathered rows from a table that
+ * fits L2: the denominator of the benchmark's L2 roofline.  sink_dev is one
+ * float that is practically never written.  No counterpart in the reference. */
+int fg_gather_probe(const float* table_dev, int64_t n_rows, int32_t row_floats,
+                    int64_t rows_per_group, int32_t n_blocks, float* sink_dev,
+                    int32_t device, void* stream);
 
 #ifdef __cplusplus
 }

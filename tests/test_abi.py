@@ -73,7 +73,12 @@ def test_shard_edges(lib):
     assert lib.fg_shard_edges(114615892, 8, b) == 0
     b = np.array(b[:])
     assert b[0] == 0 and b[-1] == 114615892
-    assert np.diff(b).max() - np.diff(b).min() <= 1
+    # equal ranges of a multiple of 32 edges; only the last one is short
+    assert (b[:-1] % 32 == 0).all() and len(set(np.diff(b)[:-1])) == 1
+    assert 0 < np.diff(b)[-1] <= np.diff(b)[0] < 114615892 / 8 + 32
+    b = _bounds(4)
+    assert lib.fg_shard_edges(40, 4, b) == 0 and list(b) == [0, 32, 40, 40, 40]
+    assert lib.fg_shard_edges(0, 4, b) == 0 and list(b) == [0, 0, 0, 0, 0]
     assert lib.fg_shard_edges(-1, 8, _bounds(8)) == 1
 
 

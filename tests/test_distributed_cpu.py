@@ -25,7 +25,7 @@ def _worker(rank, world, port, heads):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from featgraph_b200.distributed import ShardedSDDMM, ShardedSpMM
+        from featgraph_b200.distributed import ShardedSDDMM, ShardedSpMM, shard_edges
         from oracle import fg_oracle
 
         class OracleSpMM(ShardedSpMM):
@@ -66,6 +66,20 @@ def _worker(rank, world, port, heads):
         assert out.shape == want.shape
         assert np.array_equal(bits(want), bits(out)), "rank %d: SDDMM reassembly differs" % rank
 
+        # end to end from host buffers: every rank uploads 1/world of the replicated inputs
+        # and the blocks are exchanged with one all-gather; each rank "downloads" its block
+        y_host = torch.zeros(97, 32)
+        op.run_host(torch.from_numpy(x), y_host)
+        want = fg_oracle.spmm_csr_f32(adj.indptr, adj.indices, adj.data, x, n_cols=61)
+        assert np.array_equal(bits(want[op.row_lo:op.row_hi]),
+                              bits(y_host[op.row_lo:op.row_hi].numpy()))
+        o_host = torch.zeros(out.shape)
+        sd.run_host(torch.from_numpy(src), torch.from_numpy(dst), o_host)
+        want = fg_oracle.sddmm_coo_f32(coo.row, coo.col, src, dst, num_heads=heads)
+        assert np.array_equal(bits(want.reshape(out.shape)[sd.edge_lo:sd.edge_hi]),
+                              bits(o_host[sd.edge_lo:sd.edge_hi].numpy()))
+        assert list(sd.bounds) == list(shard_edges(coo.nnz, world))
+
         # more ranks than edges / rows: empty shards must not break the collectives
         tiny = random_csr(2, 5, 0.5, seed=9)
         op = OracleSpMM(tiny, 4, "cpu")
@@ -90,4 +104,66 @@ def test_single_process_bounds():
         per = np.diff(adj.indptr[b])
         assert per.sum() == adj.nnz and per.max() - adj.nnz / world <= 300
         e = shard_edges(adj.nnz, world)
-        assert e[0] == 0 and e[-1] == adj.nnz and np.diff(e).max() - np.diff(e).min() <= 1
+        assert e[0] == 0 and e[-1] == adj.nnz and (np.diff(e) >= 0).all()
+        assert (e[:-1] % 32 == 0).all() and np.diff(e).max() < adj.nnz / world + 32
+
+
+def _leaving_worker(rank, world, port, result):
+    """Rank 1 raises between two steps; rank 0's next exchange must end with an error within
+    the process group's timeout instead of blocking."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=8))
+    from featgraph_b200.distributed import ShardedSpMM
+    from oracle import fg_oracle
+
+    class OracleSpMM(ShardedSpMM):
+        def make_local(self, local_csr, schedule_args):
+            view = self._views[self.rank]
+
+            def f(x):
+                view.copy_(torch.from_numpy(fg_oracle.spmm_csr_f32(
+                    local_csr.indptr, local_csr.indices, local_csr.data, x.numpy(),
+                    n_cols=self.n_cols)))
+            return f
+
+    adj = random_csr(40, 30, 0.2, seed=3)
+    x = torch.from_numpy(features((30, 8), seed=4))
+    op = OracleSpMM(adj, 8, "cpu")
+    op.run(x)                                   # step 1: both ranks
+    if rank == 1:
+        os._exit(0)                             # leaves between steps, nothing in flight
+    t = time.time()
+    try:
+        op.run(x)                               # step 2: the peer is gone
+        result.put("no error")
+    except Exception as exc:                    # noqa: BLE001 - any error is the point
+        result.put("error after %.1f s: %s" % (time.time() - t, type(exc).__name__))
+
+
+def test_a_rank_that_leaves_between_steps_gives_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    procs = [ctx.Process(target=_leaving_worker, args=(r, 2, _free_port_once(), result))
+             for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive, "a rank blocked"
+    assert result.get(timeout=5).startswith("error")
+
+
+_PORT = []
+
+
+def _free_port_once():
+    if not _PORT:
+        _PORT.append(_free_port())
+    return _PORT[0]

@@ -163,6 +163,20 @@ def test_powerlaw_medium(oracle):
                           bits(out))
 
 
+@pytest.mark.parametrize("shape", [(64,), (8, 8)])
+def test_rmat_graph(oracle, shape):
+    # R-MAT (a, b, c, d) = (0.57, 0.19, 0.19, 0.05): another degree profile than Chung-Lu,
+    # many very short rows (tiles with more runs of equal rows than the stage has slots)
+    g = graphs.rmat_graph(scale=17, edge_draws=1 << 21, device="cuda")
+    coo = g.to_scipy().tocoo()
+    heads = shape[0] if len(shape) == 2 else 1
+    src = graphs.normal_features(g.n_cols, shape, graphs.FEAT2_SEED, "cuda").cpu().numpy()
+    dst = graphs.normal_features(g.n_rows, shape, graphs.FEAT_SEED, "cuda").cpu().numpy()
+    _, out = run_sddmm(coo, src, dst)
+    want = oracle.sddmm_coo_f32(coo.row, coo.col, src, dst, num_heads=heads, parallel=True)
+    assert np.array_equal(bits(want.reshape(out.shape)), bits(out))
+
+
 # ---- full size ------------------------------------------------------------------------------
 
 @pytest.fixture(scope="module")
@@ -201,10 +215,10 @@ def test_full_size_properties(full):
     assert torch.equal(out, want)
 
 
-@pytest.mark.parametrize("heads,dim", [(1, 64), (4, 16)])
+@pytest.mark.parametrize("heads,dim", [(1, 64), (4, 16), (1, 128), (8, 32)])
 def test_full_size_sampled_edges_against_oracle(full, oracle, heads, dim):
     g, m = full
-    shape = (g.n_cols, 64) if heads == 1 else (g.n_cols, heads, dim)
+    shape = (g.n_cols, dim) if heads == 1 else (g.n_cols, heads, dim)
     m.build([te.placeholder(shape), te.placeholder(shape)], {}, {})
     src = graphs.normal_features(g.n_cols, shape[1:], graphs.FEAT2_SEED, "cuda")
     dst = graphs.normal_features(g.n_rows, shape[1:], graphs.FEAT_SEED, "cuda")

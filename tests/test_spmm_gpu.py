@@ -188,6 +188,50 @@ def test_powerlaw_medium(oracle, feat_len):
     assert np.array_equal(bits(oracle_spmm(oracle, adj, x)), bits(y))
 
 
+@pytest.mark.parametrize("feat_len", [64, 96])
+def test_rmat_graph_with_uniform_values(oracle, feat_len):
+    # R-MAT (a, b, c, d) = (0.57, 0.19, 0.19, 0.05) with U(0,1) values: another degree
+    # profile than Chung-Lu, and values for which a fused multiply-add would show
+    g = graphs.rmat_graph(scale=17, edge_draws=1 << 21, device="cuda")
+    adj = g.to_scipy()
+    assert adj.nnz > 1500000 and 0 < adj.data.min() and adj.data.max() < 1
+    x = graphs.normal_features(g.n_cols, feat_len, graphs.FEAT_SEED, "cuda").cpu().numpy()
+    for thr in (0, 64):                    # the plan's own classes, and all three forced
+        m, y = run_spmm(adj, x, {"heavy_row_threshold": thr})
+        assert m.device_status() == 0
+        assert np.array_equal(bits(oracle_spmm(oracle, adj, x)), bits(y))
+
+
+def test_giant_kernel_gives_up_without_hanging(oracle):
+    # Every wait inside the giant-row kernel is a bounded poll.  With the limit set to zero
+    # the consumer warp cannot wait for its producers at all: the kernel must return, report
+    # through the status word and leave NaN -- never stale values -- in the rows it gave up;
+    # the next call, with the default limit, is right again and the status is clean.
+    adj = random_csr(96, 3000, 0.02, seed=77, empty_rows=(1,)).tolil()
+    rs = np.random.RandomState(78)
+    adj[3, :] = rs.random_sample(3000).astype(np.float32) + 0.5
+    adj[40, :2500] = rs.random_sample(2500).astype(np.float32) + 0.5
+    adj = adj.tocsr().astype(np.float32)
+    x = features((3000, 64), seed=79)
+    m = VanillaSpMMcuda(adj)
+    m.build([te.placeholder(x.shape)], {}, {"heavy_row_threshold": 8})
+    assert "giant: 0 rows" not in m.lower_to_ir([te.placeholder(x.shape)], {},
+                                                 {"heavy_row_threshold": 8})
+    xd = nd.array(x, m.ctx)
+    want = bits(oracle_spmm(oracle, adj, x))
+    assert np.array_equal(want, bits(m.run([xd]).asnumpy())) and m.device_status() == 0
+    m.set_poll_limit(0)
+    y = m.run([xd]).asnumpy()              # returns: nothing spins
+    with pytest.raises(_lib.FeatGraphError, match="gave up"):
+        m.device_status()
+    assert np.isnan(y[3]).all() and np.isnan(y[40]).all()          # the giant rows
+    others = np.diff(adj.indptr) <= 128    # light and heavy rows: not the giant kernel's
+    assert others.sum() == 94 and np.array_equal(want[others], bits(y)[others])
+    assert m.device_status() == 0          # reported once, then cleared
+    m.set_poll_limit(-1)
+    assert np.array_equal(want, bits(m.run([xd]).asnumpy())) and m.device_status() == 0
+
+
 def test_host_buffer_entry_point(oracle):
     adj = random_csr(300, 200, 0.1, seed=21)
     x = features((200, 64), seed=22)
@@ -239,9 +283,17 @@ def test_full_size_structure_properties(full_graph, full_module):
     assert torch.equal(y, want)
 
 
-def test_full_size_sampled_rows_against_oracle(full_graph, full_module, oracle):
-    g, m = full_graph, full_module
-    x = graphs.normal_features(g.n_cols, 64, graphs.FEAT_SEED, "cuda")
+@pytest.mark.parametrize("feat_len", [64, 128, 256])
+def test_full_size_sampled_rows_against_oracle(full_graph, full_module, oracle, feat_len):
+    # feat_len 128 and 256 get another plan on this graph than on any small one (two
+    # 64-float slabs of X per L2 residency, another light / heavy boundary)
+    g = full_graph
+    if feat_len == 64:
+        m = full_module
+    else:
+        m = VanillaSpMMcuda(g.to_scipy())
+        m.build([te.placeholder((g.n_cols, feat_len))], {}, {})
+    x = graphs.normal_features(g.n_cols, feat_len, graphs.FEAT_SEED, "cuda")
     y1 = m.run([x]).torch.clone()
     y2 = m.run([x]).torch
     assert torch.equal(y1.view(torch.int32), y2.view(torch.int32))     # run-to-run identical

@@ -4,7 +4,8 @@ It exists for hosts that may not allocate device memory once they are running (a
 in a server that owns the device pool, a loop where cudaMalloc is banned because it
 synchronises the device).  Its row-order scratch is a fixed array inside the library, shared
 by all calls and rebuilt by each, so the test makes two calls in a row, on different
-matrices, and requires both to equal the plan-based fg_spmm_csr_f32 bit for bit.
+matrices, and requires both to equal the plan-based fg_spmm_csr_f32 -- and the CPU oracle --
+bit for bit.
 
 The file is named so that pytest collects it last.
 """
@@ -15,7 +16,7 @@ import pytest
 import torch
 
 from featgraph_b200 import _lib, graphs
-from helpers import features, random_csr
+from helpers import bits, features, random_csr
 
 
 def _vp(t):
@@ -41,7 +42,7 @@ def _with_plan(lib, indptr_host, d_ptr, d_idx, d_val, x, n_rows, n_cols, feat_le
 
 
 @pytest.mark.gpu
-def test_noalloc_entry_point_equals_plan_entry_point_on_two_calls_in_a_row():
+def test_noalloc_entry_point_equals_plan_entry_point_on_two_calls_in_a_row(oracle):
     lib = _lib.load()
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     g = graphs.powerlaw_graph(n=20000, nnz_target=2000000, device="cuda")   # rows up to ~15 K long
@@ -59,6 +60,9 @@ def test_noalloc_entry_point_equals_plan_entry_point_on_two_calls_in_a_row():
                                                _vp(got), n_rows, n_cols, feat_len, 0, stream))
         torch.cuda.synchronize()
         assert torch.equal(want.view(torch.int32), got.view(torch.int32))
+        ref = oracle.spmm_csr_f32(indptr_host, d_idx.cpu().numpy(), d_val.cpu().numpy(),
+                                  x.cpu().numpy(), n_cols=n_cols)
+        assert np.array_equal(bits(ref), bits(got.cpu().numpy()))
 
 
 @pytest.mark.gpu

@@ -32,7 +32,11 @@ EXPORTED_SYMBOLS = (
     "fg_sddmm_coo_f32", "fg_sddmm_coo_f32_host", "fg_sddmm_num_launches", "fg_sddmm_describe",
     "fg_shard_rows_by_nnz", "fg_shard_edges",
     "fg_spmm_csr_f32_mcast", "fg_sddmm_coo_f32_mcast", "fg_peer_barrier", "fg_gather_probe",
+    "fg_spmm_csr_f32_general", "fg_sddmm_coo_f32_general",
 )
+
+MSG_OPS = ("mul", "add", "sub", "div", "copy_lhs", "copy_rhs")    # enum fg_msg_op
+REDUCE_OPS = ("sum", "max", "min")                                # enum fg_reduce_op
 
 
 def load():
@@ -68,6 +72,9 @@ def load():
     lib.fg_sddmm_describe.argtypes = [i64, i32, i32, ctypes.c_char_p, i64]
     lib.fg_spmm_csr_f32_mcast.argtypes = [c_void] * 7
     lib.fg_sddmm_coo_f32_mcast.argtypes = [c_void] * 5 + [i64, i64, i64, i32, i32, i32, c_void]
+    lib.fg_spmm_csr_f32_general.argtypes = [c_void] * 6 + [i32, i32, c_void]
+    lib.fg_sddmm_coo_f32_general.argtypes = [c_void] * 5 + [i64, i64, i64, i32, i32, i32, i32, i32,
+                                                            c_void]
     lib.fg_peer_barrier.argtypes = [ctypes.POINTER(c_void), i32, i32, ctypes.c_uint32, c_void,
                                     i64, i32, c_void]
     lib.fg_gather_probe.argtypes = [c_void, i64, i32, i64, i32, c_void, i32, c_void]

@@ -33,18 +33,37 @@ def is_stale():
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build_library(force=False, verbose=False):
-    """Build the library if it is missing or older than a source; returns its path."""
-    if not force and not is_stale():
+def build_library(force=False, verbose=False, defines=(), output=None):
+    """Build the library if it is missing or older than a source; returns its path.
+
+    Every source is compiled to an object file in its own nvcc process (the operator-pair
+    instantiations make spmm.cu and sddmm.cu the long poles), then the objects are linked."""
+    output = output or LIB_PATH
+    if not force and output == LIB_PATH and not is_stale():
         return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
-    cmd += ["-o", LIB_PATH] + [os.path.join(CSRC, s) for s in SOURCES]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose:
-        sys.stderr.write(res.stdout + res.stderr)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
-    return LIB_PATH
+    import tempfile
+    common = [_nvcc()] + [f for f in NVCC_FLAGS if f != "-shared"] + ["-D" + d for d in defines]
+    common += ["-Xptxas", "-v"] if verbose else []
+    with tempfile.TemporaryDirectory(prefix="fg_build_") as tmp:
+        jobs = []
+        for src in SOURCES:
+            obj = os.path.join(tmp, src.replace(".cu", ".o"))
+            cmd = common + ["-c", os.path.join(CSRC, src), "-o", obj]
+            jobs.append((cmd, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE,
+                                                    stderr=subprocess.STDOUT, text=True)))
+        objs = []
+        for cmd, obj, proc in jobs:
+            out, _ = proc.communicate()
+            if verbose:
+                sys.stderr.write(out)
+            if proc.returncode != 0:
+                raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + out)
+            objs.append(obj)
+        link = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", output]
+        res = subprocess.run(link + objs, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("link failed:\n" + " ".join(link) + "\n" + res.stdout + res.stderr)
+    return output
 
 
 if __name__ == "__main__":

@@ -20,6 +20,10 @@ namespace fg {
 // mcast != 0: p[0] is instead a MULTICAST address (an NVLink-switch multicast object that
 // maps the same buffer on every GPU of the group, this one included) and n == 1: one
 // multimem.st leaves the GPU once and the switch writes every GPU's copy.
+// Kernels take it as a `const __grid_constant__` parameter: the loop over p[] then indexes
+// the parameter where it lies (constant bank) instead of a per-thread copy in local memory
+// -- that copy cost every thread a 72-byte stack frame, whose lines, written back, were
+// two thirds of the SpMM's and half of the SDDMM's DRAM writes.
 constexpr int kMaxOutputs = 8;
 struct OutPtrs {
   float* p[kMaxOutputs];
@@ -33,6 +37,17 @@ struct PeerFlags {
   unsigned* p[kMaxOutputs];
 };
 constexpr unsigned kPeerBarrierPolls = 1u << 22;
+
+// Expands CALL(MSG, RED) for the operator pair (msg_op, reduce_op), both already range-checked.
+#define FG_DISPATCH_OPS(msg_op, reduce_op, CALL)                      \
+  switch ((msg_op) * 3 + (reduce_op)) {                               \
+    case 0: CALL(0, 0); break;   case 1: CALL(0, 1); break;   case 2: CALL(0, 2); break;   \
+    case 3: CALL(1, 0); break;   case 4: CALL(1, 1); break;   case 5: CALL(1, 2); break;   \
+    case 6: CALL(2, 0); break;   case 7: CALL(2, 1); break;   case 8: CALL(2, 2); break;   \
+    case 9: CALL(3, 0); break;   case 10: CALL(3, 1); break;  case 11: CALL(3, 2); break;  \
+    case 12: CALL(4, 0); break;  case 13: CALL(4, 1); break;  case 14: CALL(4, 2); break;  \
+    case 15: CALL(5, 0); break;  case 16: CALL(5, 1); break;  default: CALL(5, 2); break;  \
+  }
 
 // ---- host side: per-thread error message -----------------------------------
 std::string& last_error();
@@ -79,6 +94,37 @@ __device__ __forceinline__ float mul_then_add(float acc, float a, float b) {
 // results differ from the unfused ones), which would break bit-parity.
 __device__ __forceinline__ float2 mul_then_add2(float2 acc, float a, float2 b) {
   return __fadd2_rn(acc, make_float2(__fmul_rn(a, b.x), __fmul_rn(a, b.y)));
+}
+
+// ---- generalised message / reduce operators ------------------------------------
+// msg(lhs, rhs) and acc <- reduce(acc, msg); the operator numbers are those of the C ABI
+// (fg_msg_op / fg_reduce_op).  Every operation is a single correctly rounded fp32
+// instruction, never contracted; max / min are comparisons that keep the accumulator on a
+// tie and never take a NaN, so a walk in order gives the same bits as a sequential loop.
+template <int MSG>
+__device__ __forceinline__ float msg_apply(float lhs, float rhs) {
+  if (MSG == FG_MSG_MUL) return __fmul_rn(lhs, rhs);
+  if (MSG == FG_MSG_ADD) return __fadd_rn(lhs, rhs);
+  if (MSG == FG_MSG_SUB) return __fsub_rn(lhs, rhs);
+  if (MSG == FG_MSG_DIV) return __fdiv_rn(lhs, rhs);
+  if (MSG == FG_MSG_COPY_LHS) return lhs;
+  return rhs;
+}
+template <int RED>
+__device__ __forceinline__ float red_apply(float acc, float m) {
+  if (RED == FG_REDUCE_SUM) return __fadd_rn(acc, m);
+  if (RED == FG_REDUCE_MAX) return m > acc ? m : acc;
+  return m < acc ? m : acc;
+}
+template <int RED>
+__device__ __forceinline__ float red_identity() {
+  if (RED == FG_REDUCE_SUM) return 0.f;
+  // the lowest / highest finite fp32 value
+  return __int_as_float(RED == FG_REDUCE_MAX ? 0xff7fffff : 0x7f7fffff);
+}
+template <int MSG, int RED>
+__device__ __forceinline__ float combine(float acc, float lhs, float rhs) {
+  return red_apply<RED>(acc, msg_apply<MSG>(lhs, rhs));
 }
 
 // Streaming (read-once) loads of the adjacency arrays.

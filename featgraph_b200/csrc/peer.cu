@@ -16,11 +16,12 @@ namespace fg {
 // later kernels come after the acquire loads that saw every announcement.
 //
 // Every wait is bounded: after max_polls polls a thread records 1 + the rank it waited
-// for in *status (the first code sticks) and returns.  The host reads the word
-// (fg_peer_barrier_status); a barrier that gave up means a peer never arrived, and what
-// was computed around it must not be trusted.
-__global__ void peer_barrier_kernel(PeerFlags flags, int rank, int world, unsigned epoch,
-                                    int* __restrict__ status, unsigned max_polls) {
+// for in *status (the first code sticks) and returns.  The host reads the word when it
+// next synchronises; a barrier that gave up means a peer never arrived, and what was
+// computed around it must not be trusted.
+__global__ void peer_barrier_kernel(const __grid_constant__ PeerFlags flags, int rank, int world,
+                                    unsigned epoch, int* __restrict__ status,
+                                    unsigned max_polls) {
   const int t = threadIdx.x;
   if (t >= world) return;
   __threadfence_system();

@@ -45,11 +45,14 @@ constexpr int kSdRowsPerCopy = 32 / kSdLanesPerSeg;   // segments one warp-wide 
 // HEAD_DIM: the head size D when a head ends inside a chunk (D = 4, 8, ... up to
 // the chunk size), or 0 when D is a larger multiple of the chunk (heads end only at
 // chunk boundaries).
-template <int HEAD_DIM>
+// MSG / RED: the message and reduce operators (FG_MSG_MUL with FG_REDUCE_SUM is the dot
+// product of the reference; lhs = the src element, rhs = the dst element).
+template <int HEAD_DIM, int MSG, int RED>
 __global__ void __launch_bounds__(kSdWarps * 32)
 sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
                   const float* __restrict__ src, const float* __restrict__ dst,
-                  OutPtrs out, long long nnz, int F, int H, int tiles_per_warp) {
+                  const __grid_constant__ OutPtrs out, long long nnz, int F, int H,
+                  int tiles_per_warp) {
   constexpr unsigned kFull = 0xffffffffu;
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x & 31;
@@ -115,7 +118,11 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
     for (int k = 0; k < 32 / kSdRowsPerCopy; ++k) {
       const int e = lane / kSdLanesPerSeg + kSdRowsPerCopy * k;
       const int c = __shfl_sync(kFull, c_iss, e);
+#ifdef FG_SD_SRC_CA
+      cp_async16_ca(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
+#else
       cp_async16_cg(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
+#endif
     }
     if (staged) {
 #pragma unroll
@@ -137,7 +144,7 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
     if (p < total) issue(p);
     cp_async_commit();
   }
-  float acc = 0.f;
+  float acc = red_identity<RED>();
   int head = 0, chunk = 0, buf = 0, buf_issue = kSdStages - 1;
   long long e = tile0 * 32 + lane;
   for (int it = 0; it < total; ++it) {
@@ -159,26 +166,26 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
     for (int q = 0; q < kSdChunk / 4; ++q) {
       const float4 a = s4[q];
       const float4 b = d4[q];
-      acc = mul_then_add(acc, a.x, b.x);
-      acc = mul_then_add(acc, a.y, b.y);
-      acc = mul_then_add(acc, a.z, b.z);
-      acc = mul_then_add(acc, a.w, b.w);
+      acc = combine<MSG, RED>(acc, a.x, b.x);
+      acc = combine<MSG, RED>(acc, a.y, b.y);
+      acc = combine<MSG, RED>(acc, a.z, b.z);
+      acc = combine<MSG, RED>(acc, a.w, b.w);
       if (HEAD_DIM > 0 && ((q + 1) * 4) % (HEAD_DIM > 0 ? HEAD_DIM : 4) == 0) {
         if (e < nnz) out_store(out, (size_t)e * H + head, acc);
         ++head;
-        acc = 0.f;
+        acc = red_identity<RED>();
       }
     }
     ++chunk;
     if (HEAD_DIM == 0 && chunk % chunks_per_head == 0) {
       if (e < nnz) out_store(out, (size_t)e * H + head, acc);
       ++head;
-      acc = 0.f;
+      acc = red_identity<RED>();
     }
     if (chunk == n_chunks) {  // next stage belongs to the next tile
       chunk = 0;
       head = 0;
-      acc = 0.f;
+      acc = red_identity<RED>();
       e += 32;
     }
     buf = buf == kSdStages - 1 ? 0 : buf + 1;
@@ -188,10 +195,11 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
   cp_async_wait<0>();
 }
 
+template <int MSG, int RED>
 __global__ void __launch_bounds__(256)
 sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
                      const float* __restrict__ src, const float* __restrict__ dst,
-                     OutPtrs out, long long n_out, int F, int H) {
+                     const __grid_constant__ OutPtrs out, long long n_out, int F, int H) {
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= n_out) return;
   const long long e = i / H;
@@ -199,8 +207,8 @@ sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
   const int D = F / H;
   const float* s = src + (size_t)col[e] * F + (size_t)h * D;
   const float* d = dst + (size_t)row[e] * F + (size_t)h * D;
-  float acc = 0.f;
-  for (int k = 0; k < D; ++k) acc = mul_then_add(acc, s[k], d[k]);
+  float acc = red_identity<RED>();
+  for (int k = 0; k < D; ++k) acc = combine<MSG, RED>(acc, s[k], d[k]);
   out_store(out, (size_t)i, acc);
 }
 
@@ -224,7 +232,8 @@ static int sddmm_variant(int F, int H) {
 // in-kernel stores are the faster form: 0.67 against 1.01 ms per SDDMM on 8 GPUs).
 template <bool VEC>
 __global__ void __launch_bounds__(256)
-sddmm_push_kernel(const float* __restrict__ src, OutPtrs peers, long long offset, long long n) {
+sddmm_push_kernel(const float* __restrict__ src, const __grid_constant__ OutPtrs peers,
+                  long long offset, long long n) {
   const long long stride = (long long)gridDim.x * 256;
   long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (VEC) {
@@ -302,11 +311,54 @@ extern "C" int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_head
   return FG_OK;
 }
 
+namespace fg {
+
+template <int MSG, int RED>
+static cudaError_t sddmm_launch_kernels(int variant, long long grid, const int32_t* row,
+                                        const int32_t* col, const float* src, const float* dst,
+                                        const OutPtrs& out, int64_t nnz, int32_t feat_len,
+                                        int32_t num_heads, int32_t device, cudaStream_t st) {
+  if (variant < 0) {
+    sddmm_generic_kernel<MSG, RED><<<(unsigned)grid, 256, 0, st>>>(
+        row, col, src, dst, out, (long long)nnz * num_heads, feat_len, num_heads);
+    return cudaGetLastError();
+  }
+#define FG_SD_LAUNCH(HPC)                                                                     \
+  do {                                                                                        \
+    static thread_local int configured_dev = -1;                                              \
+    if (configured_dev != device) {                                                           \
+      cudaError_t e__ = cudaFuncSetAttribute(sddmm_tile_kernel<HPC, MSG, RED>,                \
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                             kSdSmemBytes);                                   \
+      if (e__ != cudaSuccess) return e__;                                                     \
+      configured_dev = device;                                                                \
+    }                                                                                         \
+    sddmm_tile_kernel<HPC, MSG, RED><<<(unsigned)grid, kSdWarps * 32, kSdSmemBytes, st>>>(    \
+        row, col, src, dst, out, nnz, feat_len, num_heads, kSdTilesPerWarp);                  \
+  } while (0)
+  switch (variant) {
+    case 0: FG_SD_LAUNCH(0); break;
+    case 4: FG_SD_LAUNCH(4); break;
+    case 8: FG_SD_LAUNCH(8); break;
+    case 16: FG_SD_LAUNCH(16); break;
+    default: FG_SD_LAUNCH(32); break;
+  }
+#undef FG_SD_LAUNCH
+  return cudaGetLastError();
+}
+
+}  // namespace fg
+
 static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src,
                         const float* dst, float* const* outs, int32_t n_outs, int mcast,
                         int64_t nnz, int64_t n_rows, int64_t n_cols, int32_t feat_len,
-                        int32_t num_heads, int32_t device, void* stream) {
+                        int32_t num_heads, int32_t device, void* stream,
+                        int32_t msg_op = FG_MSG_MUL, int32_t reduce_op = FG_REDUCE_SUM) {
   using namespace fg;
+  if (msg_op < FG_MSG_MUL || msg_op > FG_MSG_COPY_RHS || reduce_op < FG_REDUCE_SUM ||
+      reduce_op > FG_REDUCE_MIN)
+    return fail(FG_ERR_INVALID_ARGUMENT, "unknown msg_op %d or reduce_op %d", (int)msg_op,
+                (int)reduce_op);
   if (!outs || n_outs < 1 || n_outs > kMaxOutputs)
     return fail(FG_ERR_INVALID_ARGUMENT, "need 1 to %d output pointers, got %d", kMaxOutputs,
                 (int)n_outs);
@@ -335,42 +387,35 @@ static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src
   const bool aligned = (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(dst) % 16 == 0);
   const int variant = aligned ? sddmm_variant(feat_len, num_heads) : -1;
+  long long grid;
   if (variant < 0) {
-    const long long n_out = (long long)nnz * num_heads;
-    const long long grid = (n_out + 255) / 256;
+    grid = ((long long)nnz * num_heads + 255) / 256;
     if (grid >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "output too large for the generic kernel");
-    sddmm_generic_kernel<<<(unsigned)grid, 256, 0, st>>>(row, col, src, dst, out, n_out, feat_len,
-                                                         num_heads);
-    FG_CUDA_TRY(cudaGetLastError());
-    return FG_OK;
+  } else {
+    const long long tiles = (nnz + 31) / 32;
+    const long long per_cta = (long long)kSdWarps * kSdTilesPerWarp;
+    grid = (tiles + per_cta - 1) / per_cta;
+    if (grid >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "edge count too large");
   }
-
-  const long long tiles = (nnz + 31) / 32;
-  const long long per_cta = (long long)kSdWarps * kSdTilesPerWarp;
-  const long long grid = (tiles + per_cta - 1) / per_cta;
-  if (grid >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "edge count too large");
-#define FG_SD_LAUNCH(HPC)                                                                    \
-  do {                                                                                       \
-    static thread_local int configured_dev = -1;                                             \
-    if (configured_dev != device) {                                                          \
-      FG_CUDA_TRY(cudaFuncSetAttribute(sddmm_tile_kernel<HPC>,                               \
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,          \
-                                       kSdSmemBytes));                                       \
-      configured_dev = device;                                                               \
-    }                                                                                        \
-    sddmm_tile_kernel<HPC><<<(unsigned)grid, kSdWarps * 32, kSdSmemBytes, st>>>(             \
-        row, col, src, dst, out, nnz, feat_len, num_heads, kSdTilesPerWarp);                 \
-  } while (0)
-  switch (variant) {
-    case 0: FG_SD_LAUNCH(0); break;
-    case 4: FG_SD_LAUNCH(4); break;
-    case 8: FG_SD_LAUNCH(8); break;
-    case 16: FG_SD_LAUNCH(16); break;
-    default: FG_SD_LAUNCH(32); break;
-  }
-#undef FG_SD_LAUNCH
-  FG_CUDA_TRY(cudaGetLastError());
+  cudaError_t err = cudaSuccess;
+#define FG_SD_OPS(M, R)                                                                          \
+  err = sddmm_launch_kernels<M, R>(variant, grid, row, col, src, dst, out, nnz, feat_len,       \
+                                   num_heads, device, st)
+  FG_DISPATCH_OPS(msg_op, reduce_op, FG_SD_OPS);
+#undef FG_SD_OPS
+  FG_CUDA_TRY(err);
   return FG_OK;
+}
+
+extern "C" int fg_sddmm_coo_f32_general(const int32_t* row, const int32_t* col, const float* src,
+                                        const float* dst, float* out, int64_t nnz,
+                                        int64_t n_rows, int64_t n_cols, int32_t feat_len,
+                                        int32_t num_heads, int32_t msg_op, int32_t reduce_op,
+                                        int32_t device, void* stream) {
+  if (nnz > 0 && !out) return fg::fail(FG_ERR_INVALID_ARGUMENT, "null device pointer");
+  float* outs[1] = {out};
+  return sddmm_launch(row, col, src, dst, outs, 1, 0, nnz, n_rows, n_cols, feat_len, num_heads,
+                      device, stream, msg_op, reduce_op);
 }
 
 extern "C" int fg_sddmm_coo_f32_multi(const int32_t* row, const int32_t* col, const float* src,

@@ -9,24 +9,28 @@
 //
 // Rows are sorted by degree on the host (plan) and split into three classes,
 // each with its own kernel, launched on three streams so that they overlap:
-//   * light rows (deg <= max(2048, call estimate / 1100 cycles)) -> spmm_light_kernel: a group of G = W/4 lanes
-//       owns one (row, W-float feature slab); float4 gathers straight into
-//       registers, 8 in flight per lane, index/value tile fetched one iteration
-//       ahead; rows are served in descending degree so that the groups of a
-//       warp finish together.
+//   * light rows (deg <= max(2048, call estimate / 400 cycles)) -> spmm_light_kernel: a
+//       group of G = W/4 lanes owns one (row, W-float feature slab); float4 gathers
+//       straight into registers, 8 in flight per lane, index/value tile fetched one
+//       iteration ahead; rows are served in descending degree so that the groups of a
+//       warp finish together.  The cheapest path per nonzero: nothing crosses shared
+//       memory.
 //   * heavy rows -> spmm_heavy_kernel: one warp owns one (row, 32- or 64-float
 //       slab); indices/values and the gathered X segments are staged through
 //       shared memory with cp.async rings, which takes the gather latency off
 //       the sequential add chain.
-//   * giant rows (the few whose chain would outlast the rest of the call) ->
-//       spmm_giant_kernel: one CTA per (row, 32-float slab); nine producer warps
-//       gather, multiply and store transposed products into a shared-memory
+//   * giant rows (the few whose chain would outlast its share of the call) ->
+//       spmm_chain_kernel<GiantShape>: one CTA per (row, 32-float slab); nine producer
+//       warps gather, multiply and store transposed products into a shared-memory
 //       ring, one consumer warp only adds, in order, at 5.5 cycles per nonzero
 //       (the dependent fp32 add alone takes 4.2).  The longest row bounds the
 //       whole call -- its sum is one dependent chain.
 //   * anything the vector paths cannot take (feat_len not a multiple of 32,
 //     unaligned pointers) -> spmm_generic_kernel, one warp per row.
+// Every kernel is a template over a message operator and a reducer (common.cuh); multiply
+// with sum is the reference's SpMM, the other pairs are the generalised form.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -36,14 +40,19 @@ namespace fg {
 
 // ------------------------------------------------------------------ kernels --
 
-// One group of G lanes per (row, slab) item; W = 4 * G floats per slab.
-template <int G>
-__global__ void __launch_bounds__(256)
+// One group of G lanes per (row, slab) item; W = 4 * G floats per slab; U gathers of 16
+// bytes in flight per lane (a row advances U nonzeros per gather latency).
+// MSG / RED: message and reduce operators (FG_MSG_MUL with FG_REDUCE_SUM is the reference's
+// SpMM; lhs = the gathered X element, rhs = the edge value).
+template <int G, int U, int MSG, int RED>
+__global__ void __launch_bounds__(256, U <= 8 ? 4 : 2)
 spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
-                  OutPtrs Y, const int* __restrict__ rows, int n_listed,
+                  const __grid_constant__ OutPtrs Y, const int* __restrict__ rows, int n_listed,
                   long long n_items, int F) {
   constexpr unsigned kFull = 0xffffffffu;
+  constexpr int T = G > U ? G : U;  // nonzeros per index / value tile: one per lane, or two
+  constexpr int PER = T / G;        // index words per lane and tile
   const int gl = threadIdx.x % G;  // lane within the group
   const long long item = (long long)blockIdx.x * (256 / G) + threadIdx.x / G;
   const bool valid = item < n_items;
@@ -56,62 +65,81 @@ spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   }
   const size_t col_off = (size_t)slab * (4 * G) + (size_t)gl * 4;
   const float* xcol = X + col_off;
-  float2 acc_lo = make_float2(0.f, 0.f), acc_hi = make_float2(0.f, 0.f);
+  float2 acc_lo = make_float2(red_identity<RED>(), red_identity<RED>()), acc_hi = acc_lo;
+  // acc <- reduce(acc, msg(x, v)) on the lane's four features; the reference's pair takes
+  // the packed-add form
+  auto fold = [&](float vu, const float4& xv) {
+    if (MSG == FG_MSG_MUL && RED == FG_REDUCE_SUM) {
+      acc_lo = mul_then_add2(acc_lo, vu, make_float2(xv.x, xv.y));
+      acc_hi = mul_then_add2(acc_hi, vu, make_float2(xv.z, xv.w));
+    } else {
+      acc_lo.x = combine<MSG, RED>(acc_lo.x, xv.x, vu);
+      acc_lo.y = combine<MSG, RED>(acc_lo.y, xv.y, vu);
+      acc_hi.x = combine<MSG, RED>(acc_hi.x, xv.z, vu);
+      acc_hi.y = combine<MSG, RED>(acc_hi.y, xv.w, vu);
+    }
+  };
 
   // Index/value tile of the NEXT iteration, fetched one iteration ahead so that
   // its DRAM latency overlaps the gathers of the current one.
-  int idx_next = 0;
-  float v_next = 0.f;
-  if (gl < end - e) {
-    idx_next = ld_stream(indices + e + gl);
-    v_next = ld_stream(vals + e + gl);
+  int idx_next[PER];
+  float v_next[PER];
+#pragma unroll
+  for (int p = 0; p < PER; ++p) {
+    idx_next[p] = 0;
+    v_next[p] = 0.f;
+    if (p * G + gl < end - e) {
+      idx_next[p] = ld_stream(indices + e + p * G + gl);
+      v_next[p] = ld_stream(vals + e + p * G + gl);
+    }
   }
 
   // The loop is warp-uniform: groups whose row is exhausted idle (cnt <= 0).
   while (__any_sync(kFull, e < end)) {
     const int cnt = end - e;
-    const int idx = idx_next;
-    const float v = v_next;
-    idx_next = 0;
-    v_next = 0.f;
-    if (gl < cnt - G) {
-      idx_next = ld_stream(indices + e + G + gl);
-      v_next = ld_stream(vals + e + G + gl);
+    int idx[PER];
+    float v[PER];
+#pragma unroll
+    for (int p = 0; p < PER; ++p) {
+      idx[p] = idx_next[p];
+      v[p] = v_next[p];
+      idx_next[p] = 0;
+      v_next[p] = 0.f;
+      if (p * G + gl < cnt - T) {
+        idx_next[p] = ld_stream(indices + e + T + p * G + gl);
+        v_next[p] = ld_stream(vals + e + T + p * G + gl);
+      }
     }
 #pragma unroll
-    for (int j0 = 0; j0 < G; j0 += 8) {
-      float4 x[8];
-      if (__all_sync(kFull, cnt >= j0 + 8)) {
+    for (int j0 = 0; j0 < T; j0 += U) {
+      float4 x[U];
+      if (__all_sync(kFull, cnt >= j0 + U)) {
         // every group of the warp has a full batch: no predicates
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int c = __shfl_sync(kFull, idx, j0 + u, G);
+        for (int u = 0; u < U; ++u) {
+          const int c = __shfl_sync(kFull, idx[(j0 + u) / G], (j0 + u) % G, G);
           x[u] = ld_gather4(xcol + (size_t)c * F);
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const float vu = __shfl_sync(kFull, v, j0 + u, G);
-          acc_lo = mul_then_add2(acc_lo, vu, make_float2(x[u].x, x[u].y));
-          acc_hi = mul_then_add2(acc_hi, vu, make_float2(x[u].z, x[u].w));
+        for (int u = 0; u < U; ++u) {
+          const float vu = __shfl_sync(kFull, v[(j0 + u) / G], (j0 + u) % G, G);
+          fold(vu, x[u]);
         }
       } else {
         if (!__any_sync(kFull, j0 < cnt)) break;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int c = __shfl_sync(kFull, idx, j0 + u, G);
+        for (int u = 0; u < U; ++u) {
+          const int c = __shfl_sync(kFull, idx[(j0 + u) / G], (j0 + u) % G, G);
           if (j0 + u < cnt) x[u] = ld_gather4(xcol + (size_t)c * F);
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const float vu = __shfl_sync(kFull, v, j0 + u, G);
-          if (j0 + u < cnt) {
-            acc_lo = mul_then_add2(acc_lo, vu, make_float2(x[u].x, x[u].y));
-            acc_hi = mul_then_add2(acc_hi, vu, make_float2(x[u].z, x[u].w));
-          }
+        for (int u = 0; u < U; ++u) {
+          const float vu = __shfl_sync(kFull, v[(j0 + u) / G], (j0 + u) % G, G);
+          if (j0 + u < cnt) fold(vu, x[u]);
         }
       }
     }
-    if (cnt > 0) e += (cnt < G ? cnt : G);
+    if (cnt > 0) e += (cnt < T ? cnt : T);
   }
   if (valid)
     out_store(Y, (size_t)row * F + col_off, make_float4(acc_lo.x, acc_lo.y, acc_hi.x, acc_hi.y));
@@ -129,7 +157,7 @@ constexpr int heavy_smem_bytes() {
 
 // Adds one stage (cnt <= 32 gathered segments, in CSR order) to a lane's
 // accumulators; xt[e] is the segment of nonzero e, vt[e] its value.
-template <int VEC>
+template <int VEC, int MSG, int RED>
 __device__ __forceinline__ void heavy_consume_stage(const float (*xt)[32 * VEC], const float* vt,
                                                     int cnt, int lane, float& acc_a,
                                                     float& acc_b) {
@@ -142,10 +170,10 @@ __device__ __forceinline__ void heavy_consume_stage(const float (*xt)[32 * VEC],
       for (int q = 0; q < 4; ++q) {
         if (VEC == 2) {
           const float2 xv = *reinterpret_cast<const float2*>(&xt[e4 + q][lane * 2]);
-          acc_a = mul_then_add(acc_a, vv[q], xv.x);
-          acc_b = mul_then_add(acc_b, vv[q], xv.y);
+          acc_a = combine<MSG, RED>(acc_a, xv.x, vv[q]);
+          acc_b = combine<MSG, RED>(acc_b, xv.y, vv[q]);
         } else {
-          acc_a = mul_then_add(acc_a, vv[q], xt[e4 + q][lane]);
+          acc_a = combine<MSG, RED>(acc_a, xt[e4 + q][lane], vv[q]);
         }
       }
     }
@@ -153,10 +181,10 @@ __device__ __forceinline__ void heavy_consume_stage(const float (*xt)[32 * VEC],
     for (int e = 0; e < cnt; ++e) {
       if (VEC == 2) {
         const float2 xv = *reinterpret_cast<const float2*>(&xt[e][lane * 2]);
-        acc_a = mul_then_add(acc_a, vt[e], xv.x);
-        acc_b = mul_then_add(acc_b, vt[e], xv.y);
+        acc_a = combine<MSG, RED>(acc_a, xv.x, vt[e]);
+        acc_b = combine<MSG, RED>(acc_b, xv.y, vt[e]);
       } else {
-        acc_a = mul_then_add(acc_a, vt[e], xt[e][lane]);
+        acc_a = combine<MSG, RED>(acc_a, xt[e][lane], vt[e]);
       }
     }
   }
@@ -185,11 +213,11 @@ __device__ __forceinline__ void heavy_decode_item(const int* __restrict__ rows, 
 }
 
 // One warp per (heavy row, 32*VEC-float slab); VEC = floats per lane (1 or 2).
-template <int VEC>
+template <int VEC, int MSG, int RED>
 __global__ void __launch_bounds__(32)
 spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
-                  OutPtrs Y, const int* __restrict__ rows, int n_listed,
+                  const __grid_constant__ OutPtrs Y, const int* __restrict__ rows, int n_listed,
                   int subs_per_slab, int F) {
   constexpr int kSlab = 32 * VEC;                 // floats per gathered segment
   constexpr int kLanesPerRow = kSlab / 4;         // 16-byte copies per segment
@@ -256,29 +284,51 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
 
   // Two scalar chains per lane (VEC == 2) rather than one packed add: on this
   // latency-bound path the packed fp32x2 add is the slower dependency.
-  float acc_a = 0.f, acc_b = 0.f;
+  float acc_a = red_identity<RED>(), acc_b = red_identity<RED>();
   for (int i = 0; i < n_stages; ++i) {
     cp_async_wait<kHvDist - 1>();  // stage i's gathers and stage i+D's indices landed
     __syncwarp();                  // ... for every lane; stage i-1 is fully consumed
     issue_gather(i + kHvDist);
     issue_idx(i + 2 * kHvDist);
     cp_async_commit();
-    heavy_consume_stage<VEC>(xs[i & (kHvXSlots - 1)], val_s[i & (kHvISlots - 1)],
+    heavy_consume_stage<VEC, MSG, RED>(xs[i & (kHvXSlots - 1)], val_s[i & (kHvISlots - 1)],
                              min(kHvEdges, deg - i * kHvEdges), lane, acc_a, acc_b);
   }
   cp_async_wait<0>();
   heavy_store_row<VEC>(Y, (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
 }
 
-constexpr int kGtWarps = 12;      // warps per CTA; warp 0 consumes, warps 4 and 8 retire
-constexpr int kGtProducers = 9;   // producer warps per CTA (the warps with id % 4 != 0)
-constexpr int kGtGroup = 16;      // 32-nonzero blocks per group: one hand-over per group
-constexpr int kGtGroups = 3;      // ring of groups
-constexpr int kGtRing = kGtGroup * kGtGroups;  // blocks in the ring
+// Shape of a chain CTA (spmm_chain_kernel): warp 0 consumes, the others produce.
+//   WARPS      warps per CTA
+//   PRODUCERS  producer warps
+//   GROUP      32-nonzero blocks per group: one hand-over per group
+//   GROUPS     groups in the ring of products
+//   RETIRE     the warps that would share the consumer's scheduler (ids 4, 8, ...) retire
+//   MIN_CTAS   CTAs per SM the register allocation must allow
+template <int WARPS_, int PRODUCERS_, int GROUP_, int GROUPS_, bool RETIRE_, int MIN_CTAS_>
+struct ChainShape {
+  static constexpr int WARPS = WARPS_, PRODUCERS = PRODUCERS_, GROUP = GROUP_, GROUPS = GROUPS_;
+  static constexpr bool RETIRE = RETIRE_;
+  static constexpr int MIN_CTAS = MIN_CTAS_;
+  static constexpr int RING = GROUP * GROUPS;  // blocks in the ring
+  static constexpr int SMEM_BYTES = RING * kHvEdges * 32 * 4  // products, [block][feature][nonzero]
+                                    + (RING + 4) * 4;         // one flag per ring block, group counter
+  // producers prefetch their index / value blocks into L2 about 200 row blocks ahead
+  static constexpr int AHEAD = (216 / PRODUCERS + 2) / 3 * 3;
+  static_assert(RING < 32 * WARPS && GROUP % 4 == 0 && GROUP >= 8 && GROUPS >= 2, "ring / group shape");
+  static_assert(PRODUCERS == (RETIRE ? WARPS - 1 - (WARPS - 1) / 4 : WARPS - 1), "producer count");
+};
+// The giant rows: a whole SM per (row, 32-float slab), nine producers, a 48-block ring.
+using GiantShape = ChainShape<12, 9, 16, 3, true, 1>;
+// Smaller shapes (4 to 6 warps, rings of 16 to 32 blocks, two or three CTAs per SM) were
+// built and measured as the kernel of the heavy class: one 30 000-nonzero row alone walks
+// at 7.5 to 9.4 cycles per nonzero (the single-warp cp.async kernel: 24 alone, 45 beside
+// others), but every product crosses shared memory twice, the L1/shared pipe saturates
+// (75 %) at 0.17 (nonzero, 32-float slab) pairs per SM-cycle against 0.27 for the cp.async
+// kernel and 0.5 for the group kernel, and the whole SpMM was slower with them (2.04 ms at
+// best against 1.91).  So this kernel serves only the rows that need its speed.
 constexpr unsigned kGtMaxPolls = 1u << 20;     // bound of every wait for a flag
 constexpr int kGtErrProducerTimeout = 1, kGtErrConsumerTimeout = 2;
-constexpr int kGtSmemBytes = kGtRing * kHvEdges * 32 * 4   // products, [block][feature][nonzero]
-                             + (kGtRing + 4) * 4;          // one flag per ring block, group counter
 
 // Quad position of giant_kernel's product layout.  With it both the producers'
 // 16-byte stores (8 lanes = 8 feature quads, one nonzero quad) and the consumer's
@@ -320,12 +370,15 @@ __device__ __forceinline__ int giant_swizzle(int f) { return ((f >> 2) ^ f) & 7;
 // cycles per nonzero (14.3 with row-major segments and per-block mbarriers).
 // Every wait is a bounded poll (max_polls); a wait that gives up is recorded in *status
 // (the first code sticks) and the row's slab is then filled with NaN.
-__global__ void __launch_bounds__(32 * kGtWarps)
-spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
+template <class S_, int MSG, int RED>
+__global__ void __launch_bounds__(32 * S_::WARPS, S_::MIN_CTAS)
+spmm_chain_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                   const float* __restrict__ vals, const float* __restrict__ X,
-                  OutPtrs Y, const int* __restrict__ rows, int n_listed,
+                  const __grid_constant__ OutPtrs Y, const int* __restrict__ rows, int n_listed,
                   int subs_per_slab, int F, int* __restrict__ status, unsigned max_polls) {
   constexpr unsigned kFull = 0xffffffffu;
+  constexpr int kGtProducers = S_::PRODUCERS, kGtGroup = S_::GROUP, kGtGroups = S_::GROUPS;
+  constexpr int kGtRing = S_::RING;
   extern __shared__ __align__(16) unsigned char giant_smem[];
   // prod[block][feature][nonzero]: a feature's 32 products of a block are 8 quads of 4
   // consecutive nonzeros, stored at quad position q ^ giant_swizzle(feature)
@@ -344,18 +397,17 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   const int n_blocks = (deg + kHvEdges - 1) / kHvEdges;  // incl. a ragged last one
 
   if (threadIdx.x <= kGtRing) ready[threadIdx.x] = 0;  // the last one is *consumed
-  static_assert(kGtRing < 32 * kGtWarps && kGtGroup % 4 == 0 && kGtGroup >= 8, "ring / group shape");
   __syncthreads();
 
   // Warps are dealt to the SM's four schedulers round-robin by id: warps 4 and 8 would
   // share the consumer's and retire at once (measured: 5.5 cycles per nonzero this way,
   // 6.3 with producers on the consumer's scheduler).
-  if (warp > 0 && (warp & 3) == 0) return;
+  if (S_::RETIRE && warp > 0 && (warp & 3) == 0) return;
   if (warp > 0) {
     // ------------------------------------------------------------ producer --
     const int* ind = indices + beg;
     const float* val = vals + beg;
-    const int pw = warp - 1 - (warp >> 2);  // producer index 0 .. kGtProducers-1
+    const int pw = S_::RETIRE ? warp - 1 - (warp >> 2) : warp - 1;  // producer index 0 .. P-1
     const int m = lane & 7;                 // this lane's feature quad: 4m .. 4m+3
     const int g8 = (lane >> 3) * 8;         // and its nonzeros within a block: g8 .. g8+7
     const float* xbase = X + (size_t)sub * 32 + 4 * m;
@@ -398,8 +450,8 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
       float4 pr[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k)
-        pr[k] = make_float4(__fmul_rn(vs[k], x[k].x), __fmul_rn(vs[k], x[k].y),
-                            __fmul_rn(vs[k], x[k].z), __fmul_rn(vs[k], x[k].w));
+        pr[k] = make_float4(msg_apply<MSG>(x[k].x, vs[k]), msg_apply<MSG>(x[k].y, vs[k]),
+                            msg_apply<MSG>(x[k].z, vs[k]), msg_apply<MSG>(x[k].w, vs[k]));
       if (grp != entered) {
         if (grp >= kGtGroups) {  // the ring block has held group grp - kGtGroups: handed back?
           int got = 0;
@@ -461,9 +513,9 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
       load_iv(u + 3, ca, va);
       load_iv(u + 4, cb, vb);
       load_iv(u + 5, cc, vc);
-      prefetch_iv(u + 24);
-      prefetch_iv(u + 25);
-      prefetch_iv(u + 26);
+      prefetch_iv(u + S_::AHEAD);
+      prefetch_iv(u + S_::AHEAD + 1);
+      prefetch_iv(u + S_::AHEAD + 2);
       emit(u, vsa, xa);
       if (u + 1 < my_blocks && ok) emit(u + 1, vsb, xb);
       if (u + 2 < my_blocks && ok) emit(u + 2, vsc, xc);
@@ -475,7 +527,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   // -------------------------------------------------------------- consumer --
   // lane = feature.  Block j lives in register set j % 4; blocks j+1 .. j+3 are
   // on their way from shared memory while block j is added.
-  float acc = 0.f;
+  float acc = red_identity<RED>();
   const int n_full = deg / kHvEdges;
   // Every lane reads the flag itself (a broadcast): a relaxed load long before the
   // check, so that the check costs a compare; the fence behind a successful check
@@ -514,19 +566,19 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       sf[q] = *reinterpret_cast<const float4*>(src + ((q ^ swz) << 2));
-      acc = __fadd_rn(acc, sa[q].x);
-      acc = __fadd_rn(acc, sa[q].y);
-      acc = __fadd_rn(acc, sa[q].z);
-      acc = __fadd_rn(acc, sa[q].w);
+      acc = red_apply<RED>(acc, sa[q].x);
+      acc = red_apply<RED>(acc, sa[q].y);
+      acc = red_apply<RED>(acc, sa[q].z);
+      acc = red_apply<RED>(acc, sa[q].w);
     }
   };
   auto chain = [&](const float4 (&sa)[8]) {
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      acc = __fadd_rn(acc, sa[q].x);
-      acc = __fadd_rn(acc, sa[q].y);
-      acc = __fadd_rn(acc, sa[q].z);
-      acc = __fadd_rn(acc, sa[q].w);
+      acc = red_apply<RED>(acc, sa[q].x);
+      acc = red_apply<RED>(acc, sa[q].y);
+      acc = red_apply<RED>(acc, sa[q].z);
+      acc = red_apply<RED>(acc, sa[q].w);
     }
   };
   // One block with its own flag check: the row's tail.
@@ -594,7 +646,7 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     await(n_full, 0u);
     const float* src = prod[n_full % kGtRing][lane];
     const int cnt = deg - n_full * kHvEdges;
-    for (int e = 0; e < cnt; ++e) acc = __fadd_rn(acc, src[(((e >> 2) ^ swz) << 2) | (e & 3)]);
+    for (int e = 0; e < cnt; ++e) acc = red_apply<RED>(acc, src[(((e >> 2) ^ swz) << 2) | (e & 3)]);
   }
   if (__any_sync(kFull, gave_up)) {
     // No sum to report: the slab is filled with NaN so that a stale value of an earlier
@@ -607,20 +659,21 @@ spmm_giant_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
 }
 
 // Fallback for any feat_len / alignment: one warp per row, lanes over features.
+template <int MSG, int RED>
 __global__ void __launch_bounds__(256)
 spmm_generic_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                     const float* __restrict__ vals, const float* __restrict__ X,
-                    OutPtrs Y, long long n_rows, int F) {
+                    const __grid_constant__ OutPtrs Y, long long n_rows, int F) {
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   const int beg = indptr[row], end = indptr[row + 1];
   for (int f0 = 0; f0 < F; f0 += 32) {
     const int f = f0 + lane;
-    float acc = 0.f;
+    float acc = red_identity<RED>();
     if (f < F) {
       for (int e = beg; e < end; ++e)
-        acc = mul_then_add(acc, vals[e], X[(size_t)indices[e] * F + f]);
+        acc = combine<MSG, RED>(acc, X[(size_t)indices[e] * F + f], vals[e]);
       out_store(Y, (size_t)row * F + f, acc);
     }
   }
@@ -643,7 +696,7 @@ struct fg_spmm_plan {
   int64_t max_deg = 0, giant_nnz = 0, heavy_nnz = 0;
   int* rows_dev = nullptr;    // the whole sorted list
   int* status_dev = nullptr;  // set by a giant-kernel wait that gave up
-  unsigned poll_limit = 0;    // polls a giant-kernel wait makes before it gives up
+  unsigned poll_limit = 0;    // polls a chain-kernel wait makes before it gives up
   cudaStream_t aux_giant = nullptr, aux_heavy = nullptr;
   cudaEvent_t fork_ev = nullptr, join_giant = nullptr, join_heavy = nullptr;
   int l2_bytes = 0, n_sms = 0;
@@ -657,8 +710,11 @@ constexpr int kMinGiantThreshold = 4096;
 // SpMM moves 50 (nonzero, 32-float slab) pairs per cycle on 148 SMs; the heavy kernel
 // walks one row at 47 cycles per nonzero, the giant kernel at 5.6.
 constexpr double kCyclesPerNnzSlab = 0.0197, kHeavyCyclesPerNnz = 47.0, kGiantCyclesPerNnz = 5.6;
-// light/heavy boundary = estimated call time in cycles / this (4096 nonzeros for a 4.5 M-cycle call)
-constexpr double kLightCyclesPerNnzOfCall = 1100.0;
+// light/heavy boundary = estimated time of one residency-slab pass in cycles / this (11 289
+// nonzeros for the 4.5 M-cycle estimate of the full graph at feat_len 64)
+constexpr double kLightCyclesPerNnzOfPass = 400.0;
+// heavy/giant boundary: rows whose chain in the heavy kernel would outlast this share of the call
+constexpr double kGiantShareOfCall = 0.45;
 
 static void plan_release(fg_spmm_plan* p) {
   if (!p) return;
@@ -775,25 +831,33 @@ static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, in
   p->heavy_vec = (p->slab_w % 64 == 0) ? 2 : 1;
   {
     // Giant class: the rows whose add chain, walked by the heavy kernel's single warp,
-    // would last more than 0.6 of the call (measured on the full graph: 0.35 -> 2.39 ms,
-    // 0.5 -> 2.33, 0.7 -> 2.29, 1.0 -> 2.91).  The call is estimated as the longer of
+    // would last more than kGiantShareOfCall of the call.  The call is estimated as the longer of
     // its throughput time and the longest row's chain in the giant kernel; a shard of
     // a multi-GPU run has less of the former, so more of its rows turn giant.  The
     // giant kernel gives an SM to 32 floats of one row, so it is kept for such rows.
     const double t_throughput = (double)p->nnz * (feat_len / 32.0) * kCyclesPerNnzSlab * 148.0 /
                                 std::max(1, p->n_sms);
     const double t_call = std::max(t_throughput, (double)max_deg * kGiantCyclesPerNnz);
-    // Heavy class: the light kernel moves more nonzeros per SM-cycle than the heavy one
-    // (0.45 against 0.26) but walks a row at about one gather latency per 8 nonzeros, so it
-    // keeps every row whose walk fits well inside the call.  Measured on the full graph at
-    // feat_len 64, ms per call by threshold, with an SDDMM between the calls as in a GNN
-    // layer (X starts cold in L2): 2048: 2.36, 3072: 2.28, 4096: 2.28, 6144: 2.40, 8192:
-    // 2.43; back to back (X stays in L2) larger is better: 4096: 2.33, 8192: 2.13, 12288:
-    // 2.11.  The boundary is set for the first case.
+    // the light kernel serves its items one residency slab after the other, so a light row
+    // has to fit one such pass, not the whole call
+    const double t_pass = t_call * p->slab_w / feat_len;
+    double light_div = kLightCyclesPerNnzOfPass, giant_share = kGiantShareOfCall;
+#ifdef FG_TUNING
+    if (const char* e = getenv("FG_LIGHT_DIV")) light_div = atof(e);
+    if (const char* e = getenv("FG_GIANT_FRAC")) giant_share = atof(e);
+#endif
+    // Heavy class: the light kernel moves about twice the nonzeros per SM-cycle of the heavy
+    // one (its gathers go straight to registers; the heavy and giant kernels pass every
+    // gathered byte through shared memory) but walks a row at about one gather latency per 8
+    // nonzeros, so it keeps every row whose walk fits inside the call.  Measured on the full
+    // graph at feat_len 64 with an SDDMM between the calls, as in a GNN layer (ms per call;
+    // light boundary / giant boundary in nonzeros): 4105 / 57648: 2.18, 8210 / 57648: 2.11,
+    // 8210 / 38432: 2.01, 11289 / 43236: 1.91, 11289 / 38432: 1.92, 12204 / 43236: 1.92,
+    // 11289 / 28824: 1.98, 15052 / 38432: 2.12, 22579 / 57648: 2.56.
     if (heavy_threshold <= 0)
       p->heavy_threshold = (int)std::min<double>(
-          1 << 20, std::max<double>(kDefaultHeavyThreshold, t_call / kLightCyclesPerNnzOfCall));
-    const double by_time = 0.6 * t_call / kHeavyCyclesPerNnz;
+          1 << 20, std::max<double>(kDefaultHeavyThreshold, t_pass / light_div));
+    const double by_time = giant_share * t_call / kHeavyCyclesPerNnz;
     int64_t thr = (int64_t)std::min(by_time, 1e9);
     thr = std::max<int64_t>(thr, kMinGiantThreshold);
     // an explicit heavy threshold (tests use tiny ones) scales the giant class down with it
@@ -835,21 +899,12 @@ static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, in
       FG_PLAN_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
       FG_PLAN_TRY(cudaEventCreateWithFlags(&p->fork_ev, cudaEventDisableTiming));
       if (p->n_giant > 0) {
-        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_giant_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kGtSmemBytes));
         FG_PLAN_TRY(cudaStreamCreateWithPriority(&p->aux_giant, cudaStreamNonBlocking, hi));
         FG_PLAN_TRY(cudaEventCreateWithFlags(&p->join_giant, cudaEventDisableTiming));
-        FG_PLAN_TRY(cudaMalloc(&p->status_dev, sizeof(int)));
-        FG_PLAN_TRY(cudaMemset(p->status_dev, 0, sizeof(int)));
       }
+      FG_PLAN_TRY(cudaMalloc(&p->status_dev, sizeof(int)));
+      FG_PLAN_TRY(cudaMemset(p->status_dev, 0, sizeof(int)));
       if (p->n_heavy > 0) {
-        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_heavy_kernel<1>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         heavy_smem_bytes<1>()));
-        FG_PLAN_TRY(cudaFuncSetAttribute(spmm_heavy_kernel<2>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         heavy_smem_bytes<2>()));
         FG_PLAN_TRY(cudaStreamCreateWithPriority(&p->aux_heavy, cudaStreamNonBlocking, hi));
         FG_PLAN_TRY(cudaEventCreateWithFlags(&p->join_heavy, cudaEventDisableTiming));
       }
@@ -893,7 +948,7 @@ extern "C" int fg_spmm_plan_status(const fg_spmm_plan* p, int32_t* device_status
   if (v != 0) {
     // reported once: the word is cleared so that later calls are judged on their own
     FG_CUDA_TRY(cudaMemset(p->status_dev, 0, sizeof(int)));
-    return fail(FG_ERR_CUDA, "spmm_giant_kernel: a bounded wait gave up (code %d: %s warp); "
+    return fail(FG_ERR_CUDA, "spmm_chain_kernel: a bounded wait gave up (code %d: %s warp); "
                 "the rows it was summing hold NaN", v,
                 v == kGtErrProducerTimeout ? "producer" : "consumer");
   }
@@ -925,14 +980,14 @@ extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t b
              "slab_w=%d | light: %d rows (deg<=%d) -> spmm_light_kernel<G=%d> grid=%lld x 256 thr | "
              "heavy: %d rows (deg<=%d), %lld nnz -> spmm_heavy_kernel<VEC=%d> grid=%lld x 32 thr, "
              "%d-stage cp.async ring, own stream | giant: %d rows, %lld nnz -> "
-             "spmm_giant_kernel grid=%lld x %d thr (%d producer warps + 1 consumer, "
+             "spmm_chain_kernel grid=%lld x %d thr (%d producer warps + 1 consumer, "
              "%d-block ring of products, flag words), own stream",
              (long long)p->n_rows, (long long)p->n_cols, (long long)p->nnz, p->feat_len,
              (long long)p->max_deg, p->l2_bytes, p->slab_w, p->n_light, p->heavy_threshold, G,
              (light_items + 256 / G - 1) / (256 / G), p->n_heavy, p->giant_threshold,
              (long long)p->heavy_nnz, p->heavy_vec, (long long)p->n_heavy * hv_slabs, kHvXSlots,
              p->n_giant, (long long)p->giant_nnz, (long long)p->n_giant * (p->feat_len / 32),
-             32 * kGtWarps, kGtProducers, kGtRing);
+             32 * GiantShape::WARPS, GiantShape::PRODUCERS, GiantShape::RING);
   } else {
     snprintf(buf, (size_t)buf_len,
              "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d | spmm_generic_kernel "
@@ -947,49 +1002,68 @@ extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t b
 
 namespace fg {
 
-template <int G>
-static void launch_light(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
-                         const float* vals, const float* x, const OutPtrs& y, cudaStream_t st) {
-  const long long items = (long long)p->n_light * (p->feat_len / (4 * G));
-  const long long grid = (items + 256 / G - 1) / (256 / G);
-  spmm_light_kernel<G><<<(unsigned)grid, 256, 0, st>>>(
-      indptr, indices, vals, x, y, p->rows_dev + p->n_giant + p->n_heavy, p->n_light, items,
-      p->feat_len);
+// Raises the dynamic shared-memory limit of one kernel instantiation, once per device
+// (and host thread).
+template <auto Kernel>
+static cudaError_t ensure_smem(int bytes, int device) {
+  static thread_local int configured_dev = -1;
+  if (configured_dev == device) return cudaSuccess;
+  const cudaError_t e =
+      cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) configured_dev = device;
+  return e;
 }
 
-}  // namespace fg
+// Launches the group-per-row kernel over `n_listed` rows of the plan's list from `first`.
+template <int G, int U, int MSG, int RED>
+static void launch_light(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
+                         const float* vals, const float* x, const OutPtrs& y, int first,
+                         int n_listed, cudaStream_t st) {
+  const long long items = (long long)n_listed * (p->feat_len / (4 * G));
+  const long long grid = (items + 256 / G - 1) / (256 / G);
+  spmm_light_kernel<G, U, MSG, RED><<<(unsigned)grid, 256, 0, st>>>(
+      indptr, indices, vals, x, y, p->rows_dev + first, n_listed, items, p->feat_len);
+}
 
-static int spmm_launch(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
-                       const float* vals, const float* x, float* const* ys, int32_t n_ys,
-                       int mcast, void* stream) {
-  using namespace fg;
-  if (!p) return fail(FG_ERR_INVALID_ARGUMENT, "plan is null");
-  if (!ys || n_ys < 1 || n_ys > kMaxOutputs)
-    return fail(FG_ERR_INVALID_ARGUMENT, "need 1 to %d output pointers, got %d", kMaxOutputs,
-                (int)n_ys);
-  if (p->n_rows == 0) return FG_OK;
-  OutPtrs y;
-  y.n = n_ys;
-  y.mcast = mcast;
-  bool aligned = reinterpret_cast<uintptr_t>(x) % 16 == 0;
-  for (int q = 0; q < kMaxOutputs; ++q) {
-    y.p[q] = q < n_ys ? ys[q] : nullptr;
-    if (q < n_ys && !ys[q]) return fail(FG_ERR_INVALID_ARGUMENT, "output pointer %d is null", q);
-    if (q < n_ys && reinterpret_cast<uintptr_t>(ys[q]) % 16 != 0) aligned = false;
-  }
-  if (!indptr) return fail(FG_ERR_INVALID_ARGUMENT, "indptr_dev is null");
-  if (p->nnz > 0 && (!indices || !vals || !x))
-    return fail(FG_ERR_INVALID_ARGUMENT, "indices_dev, vals_dev or x_dev is null");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  DeviceGuard guard(p->device);
-  if (guard.status != cudaSuccess)
-    return fail(FG_ERR_CUDA, "cannot select device %d: %s", p->device,
-                cudaGetErrorString(guard.status));
+template <class Shape, int MSG, int RED>
+static cudaError_t launch_chain(const fg_spmm_plan* p, const int32_t* indptr,
+                                const int32_t* indices, const float* vals, const float* x,
+                                const OutPtrs& y, int first, int n_listed, cudaStream_t st) {
+  const cudaError_t e =
+      ensure_smem<spmm_chain_kernel<Shape, MSG, RED>>(Shape::SMEM_BYTES, p->device);
+  if (e != cudaSuccess) return e;
+  // one CTA per (row, 32-float slab)
+  const unsigned grid = (unsigned)(n_listed * (p->feat_len / 32));
+  spmm_chain_kernel<Shape, MSG, RED><<<grid, 32 * Shape::WARPS, Shape::SMEM_BYTES, st>>>(
+      indptr, indices, vals, x, y, p->rows_dev + first, n_listed, p->slab_w / 32, p->feat_len,
+      p->status_dev, p->poll_limit);
+  return cudaGetLastError();
+}
 
+template <int VEC, int MSG, int RED>
+static cudaError_t launch_heavy(const fg_spmm_plan* p, const int32_t* indptr,
+                                const int32_t* indices, const float* vals, const float* x,
+                                const OutPtrs& y, cudaStream_t st) {
+  const cudaError_t e =
+      ensure_smem<spmm_heavy_kernel<VEC, MSG, RED>>(heavy_smem_bytes<VEC>(), p->device);
+  if (e != cudaSuccess) return e;
+  const int slab = 32 * VEC;
+  const long long items = (long long)p->n_heavy * (p->feat_len / slab);  // < INT32_MAX (plan)
+  spmm_heavy_kernel<VEC, MSG, RED><<<(unsigned)items, 32, heavy_smem_bytes<VEC>(), st>>>(
+      indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
+      p->feat_len);
+  return cudaGetLastError();
+}
+
+// All kernels of one call for one operator pair.
+template <int MSG, int RED>
+static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
+                           const float* vals, const float* x, const OutPtrs& y, bool aligned,
+                           cudaStream_t st) {
   if (!p->vector_ok || !aligned) {
     const long long grid = (p->n_rows + 7) / 8;
-    spmm_generic_kernel<<<(unsigned)grid, 256, 0, st>>>(indptr, indices, vals, x, y, p->n_rows,
-                                                        p->feat_len);
+    spmm_generic_kernel<MSG, RED><<<(unsigned)grid, 256, 0, st>>>(indptr, indices, vals, x, y,
+                                                                  p->n_rows, p->feat_len);
     FG_CUDA_TRY(cudaGetLastError());
     return FG_OK;
   }
@@ -998,40 +1072,29 @@ static int spmm_launch(const fg_spmm_plan* p, const int32_t* indptr, const int32
   // longest first, while the light kernel fills the rest of the machine; the
   // caller's stream joins both before the call returns control to it -- also when a
   // later launch fails, so that no kernel of this call is left writing Y unobserved.
-  const int slab = 32 * p->heavy_vec;
-  const int hv_slabs = p->feat_len / slab;
   if (p->fork_ev) FG_CUDA_TRY(cudaEventRecord(p->fork_ev, st));
   bool giant_forked = false, heavy_forked = false;
   auto launch_all = [&]() -> int {
     if (p->n_giant > 0) {
       FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_giant, p->fork_ev, 0));
-      // one CTA per (row, 32-float slab), whatever the heavy kernel's slab is
-      const unsigned grid = (unsigned)(p->n_giant * (p->feat_len / 32));
-      spmm_giant_kernel<<<grid, 32 * kGtWarps, kGtSmemBytes, p->aux_giant>>>(
-          indptr, indices, vals, x, y, p->rows_dev, p->n_giant, p->slab_w / 32, p->feat_len,
-          p->status_dev, p->poll_limit);
       giant_forked = true;
-      FG_CUDA_TRY(cudaGetLastError());
+      FG_CUDA_TRY((launch_chain<GiantShape, MSG, RED>(p, indptr, indices, vals, x, y, 0,
+                                                      p->n_giant, p->aux_giant)));
     }
     if (p->n_heavy > 0) {
       FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_heavy, p->fork_ev, 0));
-      const long long items = (long long)p->n_heavy * hv_slabs;  // < INT32_MAX: checked by the plan
-      if (p->heavy_vec == 2)
-        spmm_heavy_kernel<2><<<(unsigned)items, 32, heavy_smem_bytes<2>(), p->aux_heavy>>>(
-            indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
-            p->feat_len);
-      else
-        spmm_heavy_kernel<1><<<(unsigned)items, 32, heavy_smem_bytes<1>(), p->aux_heavy>>>(
-            indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
-            p->feat_len);
       heavy_forked = true;
-      FG_CUDA_TRY(cudaGetLastError());
+      if (p->heavy_vec == 2)
+        FG_CUDA_TRY((launch_heavy<2, MSG, RED>(p, indptr, indices, vals, x, y, p->aux_heavy)));
+      else
+        FG_CUDA_TRY((launch_heavy<1, MSG, RED>(p, indptr, indices, vals, x, y, p->aux_heavy)));
     }
     if (p->n_light > 0) {
+      const int first = p->n_giant + p->n_heavy;
       switch (p->slab_w) {
-        case 128: launch_light<32>(p, indptr, indices, vals, x, y, st); break;
-        case 64: launch_light<16>(p, indptr, indices, vals, x, y, st); break;
-        default: launch_light<8>(p, indptr, indices, vals, x, y, st); break;
+        case 128: launch_light<32, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, st); break;
+        case 64: launch_light<16, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, st); break;
+        default: launch_light<8, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, st); break;
       }
       FG_CUDA_TRY(cudaGetLastError());
     }
@@ -1052,6 +1115,55 @@ static int spmm_launch(const fg_spmm_plan* p, const int32_t* indptr, const int32
   if (join_err != cudaSuccess)
     return fail(FG_ERR_CUDA, "joining the plan's streams failed: %s", cudaGetErrorString(join_err));
   return FG_OK;
+}
+
+}  // namespace fg
+
+static int spmm_launch(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
+                       const float* vals, const float* x, float* const* ys, int32_t n_ys,
+                       int mcast, void* stream, int32_t msg_op = FG_MSG_MUL,
+                       int32_t reduce_op = FG_REDUCE_SUM) {
+  using namespace fg;
+  if (!p) return fail(FG_ERR_INVALID_ARGUMENT, "plan is null");
+  if (!ys || n_ys < 1 || n_ys > kMaxOutputs)
+    return fail(FG_ERR_INVALID_ARGUMENT, "need 1 to %d output pointers, got %d", kMaxOutputs,
+                (int)n_ys);
+  if (msg_op < FG_MSG_MUL || msg_op > FG_MSG_COPY_RHS || reduce_op < FG_REDUCE_SUM ||
+      reduce_op > FG_REDUCE_MIN)
+    return fail(FG_ERR_INVALID_ARGUMENT, "unknown msg_op %d or reduce_op %d", (int)msg_op,
+                (int)reduce_op);
+  if (p->n_rows == 0) return FG_OK;
+  OutPtrs y;
+  y.n = n_ys;
+  y.mcast = mcast;
+  bool aligned = reinterpret_cast<uintptr_t>(x) % 16 == 0;
+  for (int q = 0; q < kMaxOutputs; ++q) {
+    y.p[q] = q < n_ys ? ys[q] : nullptr;
+    if (q < n_ys && !ys[q]) return fail(FG_ERR_INVALID_ARGUMENT, "output pointer %d is null", q);
+    if (q < n_ys && reinterpret_cast<uintptr_t>(ys[q]) % 16 != 0) aligned = false;
+  }
+  if (!indptr) return fail(FG_ERR_INVALID_ARGUMENT, "indptr_dev is null");
+  if (p->nnz > 0 && (!indices || !vals || !x))
+    return fail(FG_ERR_INVALID_ARGUMENT, "indices_dev, vals_dev or x_dev is null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DeviceGuard guard(p->device);
+  if (guard.status != cudaSuccess)
+    return fail(FG_ERR_CUDA, "cannot select device %d: %s", p->device,
+                cudaGetErrorString(guard.status));
+  int rc = FG_OK;
+#define FG_SPMM_OPS(M, R) rc = spmm_launch_ops<M, R>(p, indptr, indices, vals, x, y, aligned, st)
+  FG_DISPATCH_OPS(msg_op, reduce_op, FG_SPMM_OPS);
+#undef FG_SPMM_OPS
+  return rc;
+}
+
+extern "C" int fg_spmm_csr_f32_general(const fg_spmm_plan* p, const int32_t* indptr,
+                                       const int32_t* indices, const float* vals,
+                                       const float* x, float* y, int32_t msg_op,
+                                       int32_t reduce_op, void* stream) {
+  if (p && p->n_rows > 0 && !y) return fg::fail(FG_ERR_INVALID_ARGUMENT, "y_dev is null");
+  float* ys[1] = {y};
+  return spmm_launch(p, indptr, indices, vals, x, ys, 1, 0, stream, msg_op, reduce_op);
 }
 
 extern "C" int fg_spmm_csr_f32_multi(const fg_spmm_plan* p, const int32_t* indptr,

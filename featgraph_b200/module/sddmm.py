@@ -87,7 +87,7 @@ class SDDMMbase(object):
 
         input_placeholders : [SrcFeat (num_cols, F), DstFeat (num_rows, F)], or both 3-D
             (N, H, D) for the multi-head kernel
-        compute_args : e.g. ``{'num_heads': H}``
+        compute_args : e.g. ``{'num_heads': H}``, ``{'msg_op': 'sub', 'reduce_op': 'max'}``
         schedule_args : e.g. ``{'num_cuda_blocks': n}`` (checked as in the reference, then
             a hint only)
         """
@@ -125,6 +125,17 @@ class SDDMMbase(object):
 
     def _launch(self, src, dst):
         a = self._spec.attrs
+        if (a["msg_op"], a["reduce_op"]) != ("mul", "sum"):
+            if getattr(self, "_mcast_output", None) or getattr(self, "_extra_outputs", None):
+                raise NotImplementedError("extra outputs are provided for the multiply / sum "
+                                          "operator pair only")
+            _lib.check(_lib.load().fg_sddmm_coo_f32_general(
+                ptr(self._adj_row_indices_tvm.torch), ptr(self._adj_col_indices_tvm.torch),
+                ptr(src), ptr(dst), ptr(self.out_tvm.torch), self._adj_row_indices.shape[0],
+                self._num_rows, self._num_cols, a["feat_len"], a["num_heads"],
+                _lib.MSG_OPS.index(a["msg_op"]), _lib.REDUCE_OPS.index(a["reduce_op"]),
+                self._ctx.device_id, current_stream_handle(self._ctx)))
+            return
         mcast = getattr(self, "_mcast_output", None)
         if mcast:
             import ctypes

@@ -96,7 +96,9 @@ class SpMMbase(object):
         """Fix the static shapes, plan the launch and allocate the output.
 
         input_placeholders : [SrcFeat], a placeholder of shape (num_cols, feat_len)
-        compute_args : dict of keyword arguments of the compute function (none on cuda)
+        compute_args : dict of keyword arguments of the compute function (none in the
+            reference's cuda op; here optionally ``msg_op`` / ``reduce_op``, the generalised
+            operators of ``vanilla_spmm_csr_cuda``)
         schedule_args : dict of keyword arguments of the schedule function, e.g.
             ``num_cuda_blocks`` / ``num_threads_per_cuda_block`` (accepted as hints), plus
             ``heavy_row_threshold`` (rows longer than this take the staged heavy-row kernel).
@@ -146,6 +148,17 @@ class SpMMbase(object):
         self._extra_outputs = None
 
     def _launch(self, x):
+        a = self._spec.attrs
+        if (a["msg_op"], a["reduce_op"]) != ("mul", "sum"):
+            if getattr(self, "_mcast_output", None) or getattr(self, "_extra_outputs", None):
+                raise NotImplementedError("extra outputs are provided for the multiply / sum "
+                                          "operator pair only")
+            _lib.check(_lib.load().fg_spmm_csr_f32_general(
+                self._plan, ptr(self._adj_indptr_tvm.torch), ptr(self._adj_indices_tvm.torch),
+                ptr(self._adj_vals_tvm.torch), ptr(x), ptr(self.out_tvm.torch),
+                _lib.MSG_OPS.index(a["msg_op"]), _lib.REDUCE_OPS.index(a["reduce_op"]),
+                current_stream_handle(self._ctx)))
+            return
         mcast = getattr(self, "_mcast_output", None)
         if mcast:
             _lib.check(_lib.load().fg_spmm_csr_f32_mcast(

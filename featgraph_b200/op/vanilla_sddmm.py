@@ -10,7 +10,7 @@ def _flat_feat(shape):
 
 
 def vanilla_sddmm(SrcFeat, DstFeat, Adj_row_indices, Adj_col_indices, num_feat_partitions=1,
-                  num_heads=None):
+                  num_heads=None, msg_op="mul", reduce_op="sum"):
     """Out[e] = sum_k SrcFeat[Adj_col_indices[e], k] * DstFeat[Adj_row_indices[e], k].
 
     Counterpart of vanilla_sddmm (python/featgraph/op/vanilla_sddmm.py:6-63).  SrcFeat is
@@ -19,7 +19,13 @@ def vanilla_sddmm(SrcFeat, DstFeat, Adj_row_indices, Adj_col_indices, num_feat_p
     Multi-head extension (no counterpart in the reference): with ``num_heads = H`` (or 3-D
     placeholders (N, H, D)) the feature axis is split into H heads of D and
     Out[e, h] = sum_d SrcFeat[col[e], h, d] * DstFeat[row[e], h, d], shape (nnz, H).
+
+    Generalised form (no counterpart either; the reference hard-codes Src * Dst under a sum,
+    :47): Out[e, h] = reduce_op over d ascending of msg_op(SrcFeat[col[e], h, d],
+    DstFeat[row[e], h, d]), operators as in vanilla_spmm_csr_cuda.
     """
+    from .vanilla_spmm import _check_ops
+    ops = _check_ops(msg_op, reduce_op)
     feat_len = _flat_feat(SrcFeat.shape)
     assert _flat_feat(DstFeat.shape) == feat_len, "dimension mismatch"
     num_edges = Adj_row_indices.shape[0]
@@ -38,8 +44,8 @@ def vanilla_sddmm(SrcFeat, DstFeat, Adj_row_indices, Adj_col_indices, num_feat_p
     oshape = (num_edges, num_heads) if multi else (num_edges,)
     return ComputeSpec("sddmm_coo", oshape, SrcFeat.dtype,
                        (SrcFeat, DstFeat, Adj_row_indices, Adj_col_indices),
-                       {"feat_len": feat_len, "num_heads": num_heads,
-                        "num_feat_partitions": int(num_feat_partitions)},
+                       dict(ops, feat_len=feat_len, num_heads=num_heads,
+                            num_feat_partitions=int(num_feat_partitions)),
                        name="vanilla_sddmm")
 
 

@@ -2,10 +2,26 @@
 from .spec import ComputeSpec, ScheduleSpec, no_x86
 
 
-def vanilla_spmm_csr_cuda(SrcFeat, Adj_indptr, Adj_indices, Adj_vals):
+def _check_ops(msg_op, reduce_op):
+    from .._lib import MSG_OPS, REDUCE_OPS
+    if msg_op not in MSG_OPS:
+        raise ValueError("msg_op must be one of %r, got %r" % (MSG_OPS, msg_op))
+    if reduce_op not in REDUCE_OPS:
+        raise ValueError("reduce_op must be one of %r, got %r" % (REDUCE_OPS, reduce_op))
+    return {"msg_op": msg_op, "reduce_op": reduce_op}
+
+
+def vanilla_spmm_csr_cuda(SrcFeat, Adj_indptr, Adj_indices, Adj_vals, msg_op="mul",
+                          reduce_op="sum"):
     """Out[row, f] = sum over the row's nonzeros of Adj_vals[e] * SrcFeat[Adj_indices[e], f].
 
     Counterpart of vanilla_spmm_csr_cuda (python/featgraph/op/vanilla_spmm.py:83-125).
+
+    Generalised form (no counterpart in the reference, which hard-codes multiply and sum,
+    :121): ``Out[row, f] = reduce_op over the row's nonzeros, in CSR order, of
+    msg_op(SrcFeat[Adj_indices[e], f], Adj_vals[e])`` with msg_op in mul / add / sub / div /
+    copy_lhs / copy_rhs and reduce_op in sum / max / min (max and min start from the lowest /
+    highest finite float, as TVM's te.max / te.min do).
 
     SrcFeat : placeholder, (num_src_vertices, feat_len)
     Adj_indptr : placeholder, (num_dst_vertices + 1,)
@@ -19,7 +35,8 @@ def vanilla_spmm_csr_cuda(SrcFeat, Adj_indptr, Adj_indices, Adj_vals):
     _, feat_len = SrcFeat.shape
     num_dst_vertices = Adj_indptr.shape[0] - 1
     return ComputeSpec("spmm_csr", (num_dst_vertices, feat_len), SrcFeat.dtype,
-                       (SrcFeat, Adj_indptr, Adj_indices, Adj_vals), {"feat_len": feat_len})
+                       (SrcFeat, Adj_indptr, Adj_indices, Adj_vals),
+                       dict(_check_ops(msg_op, reduce_op), feat_len=feat_len))
 
 
 def schedule_vanilla_spmm_csr_cuda(Out, num_cuda_blocks=None, num_threads_per_cuda_block=None):

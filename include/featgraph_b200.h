@@ -29,6 +29,22 @@ enum fg_status {
   FG_ERR_OUT_OF_MEMORY = 4
 };
 
+/* Operators of the generalised kernels (fg_spmm_csr_f32_general,
+ * fg_sddmm_coo_f32_general): a message msg(lhs, rhs) per nonzero and feature, and the
+ * reducer that folds the messages, in order, into one accumulator.  max / min start
+ * from the lowest / highest finite float, keep the accumulator on a tie and never take
+ * a NaN message.  The reference hard-codes FG_MSG_MUL with FG_REDUCE_SUM
+ * (python/featgraph/op/vanilla_spmm.py:53, 121; vanilla_sddmm.py:47). */
+enum fg_msg_op {
+  FG_MSG_MUL = 0,      /* lhs * rhs */
+  FG_MSG_ADD = 1,      /* lhs + rhs */
+  FG_MSG_SUB = 2,      /* lhs - rhs */
+  FG_MSG_DIV = 3,      /* lhs / rhs */
+  FG_MSG_COPY_LHS = 4, /* lhs       */
+  FG_MSG_COPY_RHS = 5  /* rhs       */
+};
+enum fg_reduce_op { FG_REDUCE_SUM = 0, FG_REDUCE_MAX = 1, FG_REDUCE_MIN = 2 };
+
 /* Message of the last failure on the calling thread ("" if none). */
 const char* fg_last_error_string(void);
 
@@ -92,6 +108,19 @@ int fg_spmm_plan_num_launches(const fg_spmm_plan* plan);
 int fg_spmm_csr_f32(const fg_spmm_plan* plan, const int32_t* indptr_dev,
                     const int32_t* indices_dev, const float* vals_dev,
                     const float* x_dev, float* y_dev, void* stream);
+
+/* Generalised SpMM: Y[r, f] = reduce, over the row's nonzeros in CSR order, of
+ * msg(X[indices[e], f], vals[e]) -- lhs is the source vertex's feature, rhs the
+ * edge's value; one fp32 accumulator per (r, f) that starts from the reducer's
+ * identity (so an empty row holds the identity: 0, or the lowest / highest finite
+ * float for max / min).  FG_MSG_MUL with FG_REDUCE_SUM is fg_spmm_csr_f32, bit
+ * for bit.  The reference calls its kernels "generalized" (README.md:6) but ships
+ * only this pair (python/featgraph/op/vanilla_spmm.py:53, 121); the other
+ * operator pairs have no counterpart there. */
+int fg_spmm_csr_f32_general(const fg_spmm_plan* plan, const int32_t* indptr_dev,
+                            const int32_t* indices_dev, const float* vals_dev,
+                            const float* x_dev, float* y_dev, int32_t msg_op,
+                            int32_t reduce_op, void* stream);
 
 /* The same SpMM with its result written to n_ys buffers at once (1 <= n_ys <= 8):
  * ys_host_array[0] is normally the caller's own Y block, the others the same block
@@ -167,6 +196,17 @@ int fg_sddmm_coo_f32(const int32_t* row_dev, const int32_t* col_dev,
                      int64_t nnz, int64_t n_rows, int64_t n_cols,
                      int32_t feat_len, int32_t num_heads, int32_t device,
                      void* stream);
+
+/* Generalised SDDMM: out[e, h] = reduce over d ascending of
+ * msg(src[col[e], h*D + d], dst[row[e], h*D + d]) -- lhs is the src element, rhs
+ * the dst element.  FG_MSG_MUL with FG_REDUCE_SUM is fg_sddmm_coo_f32, bit for bit
+ * (the reference's only pair, python/featgraph/op/vanilla_sddmm.py:47); the other
+ * pairs have no counterpart in the reference. */
+int fg_sddmm_coo_f32_general(const int32_t* row_dev, const int32_t* col_dev,
+                             const float* src_dev, const float* dst_dev, float* out_dev,
+                             int64_t nnz, int64_t n_rows, int64_t n_cols, int32_t feat_len,
+                             int32_t num_heads, int32_t msg_op, int32_t reduce_op,
+                             int32_t device, void* stream);
 
 /* The same SDDMM with its result written to n_outs buffers at once (see
  * fg_spmm_csr_f32_multi): outs_host_array[i] points at the position of this call's

@@ -190,3 +190,87 @@ int fg_oracle_sddmm_coo_f64(int64_t nnz, int32_t feat_len, int32_t num_heads,
   }
   return 0;
 }
+
+/*
+ * Generalised SpMM / SDDMM: a binary message function and a reducer in place
+ * of multiply and sum.  The reference frames its kernels as "generalized"
+ * (README.md:6) but ships only adj_val * feat_val under te.sum
+ * (python/featgraph/op/vanilla_spmm.py:53, 121) and Src * Dst under te.sum
+ * (python/featgraph/op/vanilla_sddmm.py:47); these two expressions are what is
+ * generalised here, in the same loop order, so NOTHING in the reference pins
+ * the other operator pairs -- they are defined by this restatement.
+ *
+ *   msg_op:    0 mul  lhs * rhs      3 div       lhs / rhs
+ *              1 add  lhs + rhs      4 copy_lhs  lhs
+ *              2 sub  lhs - rhs      5 copy_rhs  rhs
+ *   reduce_op: 0 sum  acc + m                      identity 0
+ *              1 max  m > acc ? m : acc            identity -FLT_MAX
+ *              2 min  m < acc ? m : acc            identity +FLT_MAX
+ * The identities of max / min are those of TVM's te.max / te.min reducers (the
+ * lowest / highest finite value of the type).  A NaN message never replaces
+ * the accumulator of max / min; ties keep the accumulator; so the result is
+ * defined for every input and, walked in order, bit-reproducible.
+ * SpMM: lhs = X[indices[e], f] (the source vertex's feature), rhs = vals[e] (the
+ * edge's value); nonzeros of a row in CSR order.  SDDMM: lhs = src[col[e], k],
+ * rhs = dst[row[e], k]; k ascending within a head.
+ */
+#include <float.h>
+
+static inline float fg_msg(int op, float lhs, float rhs) {
+  switch (op) {
+    case 0: return lhs * rhs;
+    case 1: return lhs + rhs;
+    case 2: return lhs - rhs;
+    case 3: return lhs / rhs;
+    case 4: return lhs;
+    default: return rhs;
+  }
+}
+
+static inline float fg_reduce(int op, float acc, float m) {
+  switch (op) {
+    case 0: return acc + m;
+    case 1: return m > acc ? m : acc;
+    default: return m < acc ? m : acc;
+  }
+}
+
+static inline float fg_identity(int op) { return op == 0 ? 0.0f : (op == 1 ? -FLT_MAX : FLT_MAX); }
+
+int fg_oracle_gspmm_csr_f32(int64_t n_rows, int32_t feat_len, const int32_t* indptr,
+                            const int32_t* indices, const float* vals, const float* x,
+                            float* y, int32_t msg_op, int32_t reduce_op) {
+  if (feat_len < 1 || msg_op < 0 || msg_op > 5 || reduce_op < 0 || reduce_op > 2) return 1;
+#pragma omp parallel for schedule(dynamic, 64)
+  for (int64_t row = 0; row < n_rows; ++row) {
+    float* acc = y + row * feat_len;
+    for (int64_t f = 0; f < feat_len; ++f) acc[f] = fg_identity(reduce_op);
+    for (int64_t e = indptr[row]; e < indptr[row + 1]; ++e) {
+      const float v = vals[e];
+      const float* src = x + (int64_t)indices[e] * feat_len;
+      for (int64_t f = 0; f < feat_len; ++f)
+        acc[f] = fg_reduce(reduce_op, acc[f], fg_msg(msg_op, src[f], v));
+    }
+  }
+  return 0;
+}
+
+int fg_oracle_gsddmm_coo_f32(int64_t nnz, int32_t feat_len, int32_t num_heads,
+                             const int32_t* row, const int32_t* col, const float* src,
+                             const float* dst, float* out, int32_t msg_op, int32_t reduce_op) {
+  if (feat_len < 1 || num_heads < 1 || feat_len % num_heads != 0) return 1;
+  if (msg_op < 0 || msg_op > 5 || reduce_op < 0 || reduce_op > 2) return 1;
+  const int64_t D = feat_len / num_heads;
+#pragma omp parallel for schedule(static)
+  for (int64_t e = 0; e < nnz; ++e) {
+    const float* a = src + (int64_t)col[e] * feat_len;
+    const float* b = dst + (int64_t)row[e] * feat_len;
+    for (int64_t h = 0; h < num_heads; ++h) {
+      float acc = fg_identity(reduce_op);
+      for (int64_t d = 0; d < D; ++d)
+        acc = fg_reduce(reduce_op, acc, fg_msg(msg_op, a[h * D + d], b[h * D + d]));
+      out[e * num_heads + h] = acc;
+    }
+  }
+  return 0;
+}

@@ -139,3 +139,45 @@ def sddmm_coo_f64(row, col, src, dst, num_heads=1):
     if rc != 0:
         raise ValueError("fg_oracle_sddmm_coo_f64: bad argument")
     return res.reshape(nnz) if num_heads == 1 else res
+
+
+MSG_OPS = ("mul", "add", "sub", "div", "copy_lhs", "copy_rhs")
+REDUCE_OPS = ("sum", "max", "min")
+
+
+def gspmm_csr_f32(indptr, indices, vals, x, msg_op="mul", reduce_op="sum"):
+    """Generalised SpMM: Y[r, f] = reduce over the row's nonzeros, in CSR order, of
+    msg(X[indices[e], f], vals[e]) (the operator table is in fg_oracle.c)."""
+    lib = _load()
+    lib.fg_oracle_gspmm_csr_f32.argtypes = [
+        ctypes.c_int64, ctypes.c_int32, _i32p, _i32p, _f32p, _f32p, _f32p, ctypes.c_int32,
+        ctypes.c_int32]
+    indptr, indices = _c(indptr, np.int32), _c(indices, np.int32)
+    vals, x = _c(vals, np.float32), _c(x, np.float32)
+    n_rows = indptr.shape[0] - 1
+    y = np.empty((n_rows, x.shape[1]), np.float32)
+    rc = lib.fg_oracle_gspmm_csr_f32(n_rows, x.shape[1], _p(indptr, _i32p), _p(indices, _i32p),
+                                     _p(vals, _f32p), _p(x, _f32p), _p(y, _f32p),
+                                     MSG_OPS.index(msg_op), REDUCE_OPS.index(reduce_op))
+    if rc != 0:
+        raise ValueError("fg_oracle_gspmm_csr_f32: bad argument")
+    return y
+
+
+def gsddmm_coo_f32(row, col, src, dst, num_heads=1, msg_op="mul", reduce_op="sum"):
+    """Generalised SDDMM: out[e, h] = reduce over d ascending of
+    msg(src[col[e], h, d], dst[row[e], h, d])."""
+    lib = _load()
+    lib.fg_oracle_gsddmm_coo_f32.argtypes = [
+        ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, _i32p, _i32p, _f32p, _f32p, _f32p,
+        ctypes.c_int32, ctypes.c_int32]
+    row, col = _c(row, np.int32), _c(col, np.int32)
+    src, dst = _c(src, np.float32), _c(dst, np.float32)
+    nnz, f = row.shape[0], int(np.prod(src.shape[1:]))
+    res = np.empty((nnz, num_heads), np.float32)
+    rc = lib.fg_oracle_gsddmm_coo_f32(nnz, f, int(num_heads), _p(row, _i32p), _p(col, _i32p),
+                                      _p(src, _f32p), _p(dst, _f32p), _p(res, _f32p),
+                                      MSG_OPS.index(msg_op), REDUCE_OPS.index(reduce_op))
+    if rc != 0:
+        raise ValueError("fg_oracle_gsddmm_coo_f32: bad argument")
+    return res.reshape(nnz) if num_heads == 1 else res

@@ -33,3 +33,51 @@ def sddmm_coo(row, col, src, dst, num_heads=1):
                 acc = np.float32(acc + prod)
             out[e, h] = acc
     return out.reshape(nnz) if num_heads == 1 else out
+
+
+_F32_MAX = np.finfo(np.float32).max
+
+
+def _msg(op, lhs, rhs):
+    with np.errstate(all="ignore"):
+        return {"mul": lambda: np.float32(lhs * rhs), "add": lambda: np.float32(lhs + rhs),
+                "sub": lambda: np.float32(lhs - rhs), "div": lambda: np.float32(lhs / rhs),
+                "copy_lhs": lambda: lhs, "copy_rhs": lambda: rhs}[op]()
+
+
+def _reduce(op, acc, m):
+    if op == "sum":
+        return np.float32(acc + m)
+    if op == "max":
+        return m if m > acc else acc
+    return m if m < acc else acc
+
+
+def _identity(op):
+    return np.float32({"sum": 0.0, "max": -_F32_MAX, "min": _F32_MAX}[op])
+
+
+def gspmm_csr(indptr, indices, vals, x, msg_op, reduce_op):
+    """The generalised SpMM of fg_oracle.c, one scalar operation at a time."""
+    n_rows, f = len(indptr) - 1, x.shape[1]
+    y = np.full((n_rows, f), _identity(reduce_op), np.float32)
+    for r in range(n_rows):
+        for e in range(indptr[r], indptr[r + 1]):
+            for k in range(f):
+                m = _msg(msg_op, np.float32(x[indices[e], k]), np.float32(vals[e]))
+                y[r, k] = _reduce(reduce_op, y[r, k], m)
+    return y
+
+
+def gsddmm_coo(row, col, src, dst, num_heads, msg_op, reduce_op):
+    nnz, f = len(row), src.shape[1]
+    d = f // num_heads
+    out = np.zeros((nnz, num_heads), np.float32)
+    for e in range(nnz):
+        for h in range(num_heads):
+            acc = _identity(reduce_op)
+            for k in range(h * d, (h + 1) * d):
+                acc = _reduce(reduce_op, acc, _msg(msg_op, np.float32(src[col[e], k]),
+                                                   np.float32(dst[row[e], k])))
+            out[e, h] = acc
+    return out.reshape(nnz) if num_heads == 1 else out

@@ -65,7 +65,14 @@ def test_sddmm_op_specs_and_reference_assertions():
         ops.vanilla_sddmm(te.placeholder((255, 128)), te.placeholder((127, 64)), row, col)
     mh = ops.vanilla_sddmm(te.placeholder((255, 4, 16)), te.placeholder((127, 4, 16)), row, col)
     assert mh.shape == (3238, 4) and mh.attrs == {"feat_len": 64, "num_heads": 4,
-                                                  "num_feat_partitions": 1}
+                                                  "num_feat_partitions": 1,
+                                                  "msg_op": "mul", "reduce_op": "sum"}
+    gen = ops.vanilla_sddmm(te.placeholder((255, 64)), te.placeholder((127, 64)), row, col,
+                            msg_op="sub", reduce_op="max")
+    assert (gen.attrs["msg_op"], gen.attrs["reduce_op"]) == ("sub", "max")
+    with pytest.raises(ValueError, match="msg_op"):
+        ops.vanilla_sddmm(te.placeholder((255, 64)), te.placeholder((127, 64)), row, col,
+                          msg_op="pow")
     mh2 = ops.vanilla_sddmm(te.placeholder((255, 64)), te.placeholder((127, 64)), row, col,
                             num_heads=8)
     assert mh2.shape == (3238, 8)

@@ -41,9 +41,11 @@ NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload on one GPU.
 # STATIC figures from one ncu capture (they do not follow later kernel changes until the
 # capture is repeated); other sizes and world sizes report null.
-NCU_TRAFFIC_BYTES = {"spmm": 1843.2e6 + 199.2e6, "sddmm": 1908.2e6 + 891.2e6}
-NCU_TRAFFIC_SOURCE = ("static: one ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of "
-                      "the full-size 1-GPU workload with the kernels of commit 6b594cb")
+NCU_TRAFFIC_BYTES = {"spmm": 1494.1e6 + 56.1e6, "sddmm": 1427.8e6 + 447.0e6}
+NCU_TRAFFIC_SOURCE = ("static: one ncu capture (dram__bytes_read.sum + dram__bytes_write.sum, 1 pass) "
+                      "of the full-size 1-GPU workload, summarised in "
+                      "profiles/bench_full_size_launch_list_and_dram.md; it does not follow later "
+                      "kernel changes until that capture is repeated")
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -442,14 +444,24 @@ def run_gpu(args):
     y_host = torch.empty((n, FEAT), dtype=torch.float32, pin_memory=True)
     o_host = torch.empty((nnz,), dtype=torch.float32, pin_memory=True)
     e2e_steps = max(3, min(args.steps, 10))
+    if world == 1:
+        # one GPU: the two host-buffer calls side by side on two streams (HostPair), so that
+        # one call's transfers overlap the other's kernels and the link runs both ways
+        from featgraph_b200.pipeline import HostPair
+        host_pair = HostPair(spmm.module, sddmm.module)
+
+        def e2e_step():
+            host_pair.run(x_host, y_host, y2_host, x_host, o_host)
+    else:
+        def e2e_step():
+            spmm.run_host(x_host, y_host)
+            sddmm.run_host(y2_host, x_host, o_host)
     for _ in range(2):
-        spmm.run_host(x_host, y_host)
-        sddmm.run_host(y2_host, x_host, o_host)
+        e2e_step()
     barrier()
     a = _mark(stream)
     for _ in range(e2e_steps):
-        spmm.run_host(x_host, y_host)
-        sddmm.run_host(y2_host, x_host, o_host)
+        e2e_step()
     b = _mark(stream)
     barrier()
     e2e_ms = a.elapsed_time(b)
@@ -548,7 +560,9 @@ def run_gpu(args):
                     "ms_per_step": round(e2e_ms / e2e_steps, 3), "steps": e2e_steps,
                     "note": "whole job: every replicated input crosses PCIe once (1/%d per rank, "
                             "exchanged over NVLink), every rank downloads its own block" % world
-                            if world > 1 else "fg_*_host entry points, pinned host buffers"},
+                            if world > 1 else "fg_*_host entry points on pinned host buffers, the "
+                            "SpMM call and the SDDMM call issued side by side on two streams "
+                            "(featgraph_b200.pipeline.HostPair)"},
             "gpu_launches": int(args.steps * (spmm.num_launches() + sddmm.num_launches()
                                               + (0 if world == 1 or not fused else
                                                  (2 if overlap else 4)))),

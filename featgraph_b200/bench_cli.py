@@ -76,6 +76,11 @@ def main(argv=None):
     ap.add_argument("--row-partitions", type=int, default=1,
                     help="SDDMM: the reference's 2-D edge blocking (VanillaSDDMMx86's arguments)")
     ap.add_argument("--col-partitions", type=int, default=1)
+    ap.add_argument("--sweep", action="store_true",
+                    help="run the whole configured sweep in one process: SpMM and SDDMM at feat-len "
+                         "32 ... 512, then multi-head SDDMM (4,16), (8,32), (16,64)")
+    ap.add_argument("--peer-mode", choices=["auto", "store", "mcast", "push"], default="auto",
+                    help="multi-GPU: how results reach the peers (featgraph_b200.distributed)")
     ap.add_argument("--dump-output", type=str, default=None,
                     help="save the (last) result array to this .npy file (rank 0)")
     args = ap.parse_args(argv)
@@ -89,22 +94,31 @@ def main(argv=None):
     device = torch.device("cuda", local)
     if world > 1:
         import torch.distributed as dist
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":    # its banner goes to stdout
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     g, source = _load_graph(args, device)
-    n, nnz = g.n_rows, g.nnz
+    n = g.n_rows
     records = []
-    if args.heads > 1:
-        feat_lens = [args.heads * (args.head_dim or 16)]
+    # the cases of this run: (kernel, feat_len, heads)
+    if args.sweep:
+        cases = [("spmm", f, 1) for f in (32, 64, 128, 256, 512)]
+        cases += [("sddmm", f, 1) for f in (32, 64, 128, 256, 512)]
+        cases += [("sddmm", h * d, h) for h, d in ((4, 16), (8, 32), (16, 64))]
+    elif args.heads > 1:
+        cases = [(args.kernel, args.heads * (args.head_dim or 16), args.heads)]
     else:
-        feat_lens = [int(f) for f in args.feat_len.split(",")]
-    adj = g.to_scipy() if args.kernel == "spmm" else None
-    rows = g.coo_rows() if args.kernel == "sddmm" else None
+        cases = [(args.kernel, int(f), 1) for f in args.feat_len.split(",")]
+    kernels = set(k for k, _, _ in cases)
+    adj = g.to_scipy() if "spmm" in kernels else None
+    rows = g.coo_rows() if "sddmm" in kernels else None
     cols = g.indices
-    if args.kernel == "sddmm" and hasattr(g, "edge_list"):
+    nnz_sd = g.nnz
+    if "sddmm" in kernels and hasattr(g, "edge_list"):
         rows, cols = g.edge_list
-        nnz = int(rows.shape[0])
-    if args.kernel == "sddmm" and (args.row_partitions > 1 or args.col_partitions > 1):
+        nnz_sd = int(rows.shape[0])
+    if "sddmm" in kernels and (args.row_partitions > 1 or args.col_partitions > 1):
         # the blocked edge order of util_partition_adj_coo_2d (row partition major, column
         # partition minor, row-major inside a block), computed on the device
         rows_per = max(-(-g.n_rows // args.row_partitions), 1)
@@ -114,18 +128,20 @@ def main(argv=None):
         rows, cols = rows[order].contiguous(), cols[order].contiguous()
         del key, order
 
-    for f in feat_lens:
-        shape = (args.heads, f // args.heads) if args.heads > 1 else (f,)
+    for kernel, f, heads in cases:
+        shape = (heads, f // heads) if heads > 1 else (f,)
         x = graphs.normal_features(g.n_cols, shape, graphs.FEAT_SEED, device)
-        if args.kernel == "spmm":
-            op = ShardedSpMM(adj, f, device)
+        if kernel == "spmm":
+            nnz = g.nnz
+            op = ShardedSpMM(adj, f, device, peer_mode=args.peer_mode)
             call = lambda: op.run(x)                       # noqa: E731
             alg = 4 * (n + 1) + 8 * nnz + 4 * nnz * f + 4 * n * f
         else:
+            nnz = nnz_sd
             y2 = graphs.normal_features(g.n_rows, shape, graphs.FEAT2_SEED, device)
-            op = ShardedSDDMM(rows, cols, n, g.n_cols, shape, device)
+            op = ShardedSDDMM(rows, cols, n, g.n_cols, shape, device, peer_mode=args.peer_mode)
             call = lambda: op.run(x, y2)                   # noqa: E731
-            alg = 8 * nnz + 8 * nnz * f + 4 * nnz * args.heads
+            alg = 8 * nnz + 8 * nnz * f + 4 * nnz * heads
         for _ in range(3):
             call()
         if world > 1:
@@ -137,6 +153,7 @@ def main(argv=None):
             call()
         t1.record()
         torch.cuda.synchronize(device)
+        op.device_status()                # raises if a bounded device-side wait gave up
         ms = torch.tensor([t0.elapsed_time(t1) / args.num_runs], device=device,
                           dtype=torch.float64)
         if world > 1:
@@ -146,15 +163,19 @@ def main(argv=None):
             if args.dump_output:
                 np.save(args.dump_output, op.out.cpu().numpy())
             records.append({
-                "kernel": args.kernel, "graph": source, "rows": n, "nnz": nnz, "feat_len": f,
-                "heads": args.heads, "n_gpus": world, "num_runs": args.num_runs,
+                "kernel": kernel, "graph": source, "rows": n, "nnz": nnz, "feat_len": f,
+                "heads": heads, "n_gpus": world, "num_runs": args.num_runs,
+                "gather": op.gather_mode,
                 "partitions": [args.row_partitions, args.col_partitions],
                 "ms": round(ms, 4), "gflops": round(2.0 * nnz * f / ms / 1e6, 1),
                 "alg_gbs": round(alg / ms / 1e6, 1),
                 "frac_of_8TBs": round(alg / ms / 1e6 / NOMINAL_HBM_GBS, 4),
                 "degree": g.degree_stats()})
             print(json.dumps(records[-1]), flush=True)
-        del op, x
+        del op, x, call
+        if kernel == "sddmm":
+            del y2
+        torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -201,6 +201,21 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
+// Programmatic dependent launch: lets a kernel that was launched behind this one in the
+// same stream WITH the programmatic-serialization attribute be dispatched as soon as every
+// CTA of this grid has executed this (or exited), instead of when the grid has completed.
+// Without such a dependent it does nothing.
+__device__ __forceinline__ void launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// Waits until the grids this one was programmatically launched behind have COMPLETED and
+// their stores are visible; returns at once for a normally launched grid.  A dependent that
+// never waits may complete before its predecessor; where something later in the stream
+// relies on both, ONE CTA of the dependent calls this at its end.
+__device__ __forceinline__ void wait_for_prior_grids() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---- flag words in shared memory (release / acquire at CTA scope) -------------
 // A load's result sits in a register like any other load's: the warp only waits
 // where the value is used, so a flag can be read long before it is checked (an

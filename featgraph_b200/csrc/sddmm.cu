@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(kSdWarps * 32)
 sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
                   const float* __restrict__ src, const float* __restrict__ dst,
                   const __grid_constant__ OutPtrs out, long long nnz, int F, int H,
-                  int tiles_per_warp) {
+                  int tiles_per_warp, int vec_heads) {
   constexpr unsigned kFull = 0xffffffffu;
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x & 31;
@@ -118,11 +118,11 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
     for (int k = 0; k < 32 / kSdRowsPerCopy; ++k) {
       const int e = lane / kSdLanesPerSeg + kSdRowsPerCopy * k;
       const int c = __shfl_sync(kFull, c_iss, e);
-#ifdef FG_SD_SRC_CA
-      cp_async16_ca(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
-#else
+      // .cg (no L1 allocation) although ncu shows that the bypass path brings 24 sectors per
+      // warp-wide copy across the crossbar where the four 128-byte segments hold 16 (.ca
+      // brings exactly 16): with .ca the kernel is SLOWER (3.55 against 2.81 ms at feat 64) --
+      // the L1's allocation work costs more than the extra sectors
       cp_async16_cg(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
-#endif
     }
     if (staged) {
 #pragma unroll
@@ -147,6 +147,27 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
   float acc = red_identity<RED>();
   int head = 0, chunk = 0, buf = 0, buf_issue = kSdStages - 1;
   long long e = tile0 * 32 + lane;
+  // A finished head leaves at once (one 4-byte store per lane: a warp's 32 edges lie H
+  // floats apart), or, when H is a multiple of four (vec_heads), waits for three more so
+  // that the lane stores 16 contiguous bytes -- a quarter of the store instructions and
+  // whole sectors instead of 4-byte pieces of them.
+  float4 pend = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto finish_head = [&]() {
+    if (vec_heads) {
+      switch (head & 3) {
+        case 0: pend.x = acc; break;
+        case 1: pend.y = acc; break;
+        case 2: pend.z = acc; break;
+        default:
+          pend.w = acc;
+          if (e < nnz) out_store(out, (size_t)e * H + head - 3, pend);
+      }
+    } else if (e < nnz) {
+      out_store(out, (size_t)e * H + head, acc);
+    }
+    ++head;
+    acc = red_identity<RED>();
+  };
   for (int it = 0; it < total; ++it) {
     if (it + kSdStages - 1 < total) issue(buf_issue);
     cp_async_commit();
@@ -170,18 +191,10 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
       acc = combine<MSG, RED>(acc, a.y, b.y);
       acc = combine<MSG, RED>(acc, a.z, b.z);
       acc = combine<MSG, RED>(acc, a.w, b.w);
-      if (HEAD_DIM > 0 && ((q + 1) * 4) % (HEAD_DIM > 0 ? HEAD_DIM : 4) == 0) {
-        if (e < nnz) out_store(out, (size_t)e * H + head, acc);
-        ++head;
-        acc = red_identity<RED>();
-      }
+      if (HEAD_DIM > 0 && ((q + 1) * 4) % (HEAD_DIM > 0 ? HEAD_DIM : 4) == 0) finish_head();
     }
     ++chunk;
-    if (HEAD_DIM == 0 && chunk % chunks_per_head == 0) {
-      if (e < nnz) out_store(out, (size_t)e * H + head, acc);
-      ++head;
-      acc = red_identity<RED>();
-    }
+    if (HEAD_DIM == 0 && chunk % chunks_per_head == 0) finish_head();
     if (chunk == n_chunks) {  // next stage belongs to the next tile
       chunk = 0;
       head = 0;
@@ -318,6 +331,10 @@ static cudaError_t sddmm_launch_kernels(int variant, long long grid, const int32
                                         const int32_t* col, const float* src, const float* dst,
                                         const OutPtrs& out, int64_t nnz, int32_t feat_len,
                                         int32_t num_heads, int32_t device, cudaStream_t st) {
+  // heads leave four at a time where the lane's four results are one aligned 16-byte piece
+  int vec_heads = num_heads % 4 == 0;
+  for (int q = 0; q < out.n; ++q)
+    if (reinterpret_cast<uintptr_t>(out.p[q]) % 16 != 0) vec_heads = 0;
   if (variant < 0) {
     sddmm_generic_kernel<MSG, RED><<<(unsigned)grid, 256, 0, st>>>(
         row, col, src, dst, out, (long long)nnz * num_heads, feat_len, num_heads);
@@ -334,7 +351,7 @@ static cudaError_t sddmm_launch_kernels(int variant, long long grid, const int32
       configured_dev = device;                                                                \
     }                                                                                         \
     sddmm_tile_kernel<HPC, MSG, RED><<<(unsigned)grid, kSdWarps * 32, kSdSmemBytes, st>>>(    \
-        row, col, src, dst, out, nnz, feat_len, num_heads, kSdTilesPerWarp);                  \
+        row, col, src, dst, out, nnz, feat_len, num_heads, kSdTilesPerWarp, vec_heads);       \
   } while (0)
   switch (variant) {
     case 0: FG_SD_LAUNCH(0); break;

@@ -8,7 +8,9 @@
 // nonzeros.
 //
 // Rows are sorted by degree on the host (plan) and split into three classes,
-// each with its own kernel, launched on three streams so that they overlap:
+// each with its own kernel; the three are launched back to back in one stream, giant rows
+// first, each dispatched behind the one before it without waiting for it to complete
+// (programmatic dependent launch), so that they overlap:
 //   * light rows (deg <= max(2048, call estimate / 400 cycles)) -> spmm_light_kernel: a
 //       group of G = W/4 lanes owns one (row, W-float feature slab); float4 gathers
 //       straight into registers, 8 in flight per lane, index/value tile fetched one
@@ -143,6 +145,10 @@ spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   }
   if (valid)
     out_store(Y, (size_t)row * F + col_off, make_float4(acc_lo.x, acc_lo.y, acc_hi.x, acc_hi.y));
+  // This grid may have been dispatched behind the heavy / giant kernels of the same call
+  // without waiting for them; its last CTA stays until they have completed, so that "this
+  // grid is complete" means "the whole SpMM is complete" to whatever follows in the stream.
+  if (blockIdx.x == gridDim.x - 1) wait_for_prior_grids();
 }
 
 constexpr int kHvEdges = 32;    // nonzeros per stage
@@ -229,6 +235,7 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   float(*val_s)[kHvEdges] = reinterpret_cast<float(*)[kHvEdges]>(
       heavy_smem + kHvXSlots * kHvEdges * kSlab * 4 + kHvISlots * kHvEdges * 4);
 
+  launch_dependents();  // the next kernel of the call may be dispatched behind this CTA
   const int lane = threadIdx.x;
   int row, sub;
   heavy_decode_item(rows, n_listed, subs_per_slab, row, sub);
@@ -296,6 +303,7 @@ spmm_heavy_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   }
   cp_async_wait<0>();
   heavy_store_row<VEC>(Y, (size_t)row * F + (size_t)sub * kSlab, lane, acc_a, acc_b);
+  if (blockIdx.x == gridDim.x - 1) wait_for_prior_grids();  // as in spmm_light_kernel
 }
 
 // Shape of a chain CTA (spmm_chain_kernel): warp 0 consumes, the others produce.
@@ -319,7 +327,11 @@ struct ChainShape {
   static_assert(PRODUCERS == (RETIRE ? WARPS - 1 - (WARPS - 1) / 4 : WARPS - 1), "producer count");
 };
 // The giant rows: a whole SM per (row, 32-float slab), nine producers, a 48-block ring.
-using GiantShape = ChainShape<12, 9, 16, 3, true, 1>;
+#ifndef FG_GT_GROUP
+#define FG_GT_GROUP 16
+#define FG_GT_GROUPS 3
+#endif
+using GiantShape = ChainShape<12, 9, FG_GT_GROUP, FG_GT_GROUPS, true, 1>;
 // Smaller shapes (4 to 6 warps, rings of 16 to 32 blocks, two or three CTAs per SM) were
 // built and measured as the kernel of the heavy class: one 30 000-nonzero row alone walks
 // at 7.5 to 9.4 cycles per nonzero (the single-warp cp.async kernel: 24 alone, 45 beside
@@ -377,6 +389,7 @@ spmm_chain_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
                   const __grid_constant__ OutPtrs Y, const int* __restrict__ rows, int n_listed,
                   int subs_per_slab, int F, int* __restrict__ status, unsigned max_polls) {
   constexpr unsigned kFull = 0xffffffffu;
+  launch_dependents();  // the next kernel of the call may be dispatched behind this CTA
   constexpr int kGtProducers = S_::PRODUCERS, kGtGroup = S_::GROUP, kGtGroups = S_::GROUPS;
   constexpr int kGtRing = S_::RING;
   extern __shared__ __align__(16) unsigned char giant_smem[];
@@ -533,7 +546,11 @@ spmm_chain_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   // check, so that the check costs a compare; the fence behind a successful check
   // turns it into an acquire (every lane's loads of the block come after it).  A lane
   // whose bounded wait gives up only notes it; the warp looks at the notes at the end.
+#if defined(FG_GT_DIAG)
+  auto peek = [&](int j) { return (unsigned)j + 1u; };  // timing diagnosis only: no flag loads
+#else
   auto peek = [&](int j) { return ld_relaxed_shared(&ready[j % kGtRing]); };
+#endif
   bool gave_up = false;
   auto await = [&](int j, unsigned seen) {
     const unsigned want = (unsigned)j + 1u;
@@ -697,8 +714,6 @@ struct fg_spmm_plan {
   int* rows_dev = nullptr;    // the whole sorted list
   int* status_dev = nullptr;  // set by a giant-kernel wait that gave up
   unsigned poll_limit = 0;    // polls a chain-kernel wait makes before it gives up
-  cudaStream_t aux_giant = nullptr, aux_heavy = nullptr;
-  cudaEvent_t fork_ev = nullptr, join_giant = nullptr, join_heavy = nullptr;
   int l2_bytes = 0, n_sms = 0;
 };
 
@@ -721,11 +736,6 @@ static void plan_release(fg_spmm_plan* p) {
   DeviceGuard g(p->device);
   if (p->rows_dev) cudaFree(p->rows_dev);
   if (p->status_dev) cudaFree(p->status_dev);
-  if (p->fork_ev) cudaEventDestroy(p->fork_ev);
-  if (p->join_giant) cudaEventDestroy(p->join_giant);
-  if (p->join_heavy) cudaEventDestroy(p->join_heavy);
-  if (p->aux_giant) cudaStreamDestroy(p->aux_giant);
-  if (p->aux_heavy) cudaStreamDestroy(p->aux_heavy);
   delete p;
 }
 
@@ -894,20 +904,9 @@ static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, in
     FG_PLAN_TRY(cudaMalloc(&p->rows_dev, sizeof(int32_t) * (size_t)n_rows));
     FG_PLAN_TRY(cudaMemcpy(p->rows_dev, order.data(), sizeof(int32_t) * (size_t)n_rows,
                            cudaMemcpyHostToDevice));
-    if (p->n_giant + p->n_heavy > 0) {
-      int lo = 0, hi = 0;
-      FG_PLAN_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-      FG_PLAN_TRY(cudaEventCreateWithFlags(&p->fork_ev, cudaEventDisableTiming));
-      if (p->n_giant > 0) {
-        FG_PLAN_TRY(cudaStreamCreateWithPriority(&p->aux_giant, cudaStreamNonBlocking, hi));
-        FG_PLAN_TRY(cudaEventCreateWithFlags(&p->join_giant, cudaEventDisableTiming));
-      }
+    if (p->n_giant > 0) {
       FG_PLAN_TRY(cudaMalloc(&p->status_dev, sizeof(int)));
       FG_PLAN_TRY(cudaMemset(p->status_dev, 0, sizeof(int)));
-      if (p->n_heavy > 0) {
-        FG_PLAN_TRY(cudaStreamCreateWithPriority(&p->aux_heavy, cudaStreamNonBlocking, hi));
-        FG_PLAN_TRY(cudaEventCreateWithFlags(&p->join_heavy, cudaEventDisableTiming));
-      }
     }
   }
 #undef FG_PLAN_TRY
@@ -979,9 +978,10 @@ extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t b
              "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d max_deg=%lld | L2=%d B "
              "slab_w=%d | light: %d rows (deg<=%d) -> spmm_light_kernel<G=%d> grid=%lld x 256 thr | "
              "heavy: %d rows (deg<=%d), %lld nnz -> spmm_heavy_kernel<VEC=%d> grid=%lld x 32 thr, "
-             "%d-stage cp.async ring, own stream | giant: %d rows, %lld nnz -> "
+             "%d-stage cp.async ring | giant: %d rows, %lld nnz -> "
              "spmm_chain_kernel grid=%lld x %d thr (%d producer warps + 1 consumer, "
-             "%d-block ring of products, flag words), own stream",
+             "%d-block ring of products, flag words); launch order giant, heavy, light, "
+             "programmatic dependent launches",
              (long long)p->n_rows, (long long)p->n_cols, (long long)p->nnz, p->feat_len,
              (long long)p->max_deg, p->l2_bytes, p->slab_w, p->n_light, p->heavy_threshold, G,
              (light_items + 256 / G - 1) / (256 / G), p->n_heavy, p->giant_threshold,
@@ -1014,45 +1014,66 @@ static cudaError_t ensure_smem(int bytes, int device) {
   return e;
 }
 
+// One kernel launch; `programmatic`: the kernel may be dispatched as soon as every CTA of
+// the kernel before it in the stream has let its dependents go (launch_dependents()),
+// instead of when that kernel has completed.
+template <typename... Params, typename... Args>
+static cudaError_t launch_kernel(void (*kernel)(Params...), unsigned grid, unsigned block,
+                                 size_t smem, cudaStream_t st, bool programmatic, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = programmatic ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 // Launches the group-per-row kernel over `n_listed` rows of the plan's list from `first`.
 template <int G, int U, int MSG, int RED>
-static void launch_light(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
-                         const float* vals, const float* x, const OutPtrs& y, int first,
-                         int n_listed, cudaStream_t st) {
+static cudaError_t launch_light(const fg_spmm_plan* p, const int32_t* indptr,
+                                const int32_t* indices, const float* vals, const float* x,
+                                const OutPtrs& y, int first, int n_listed, cudaStream_t st,
+                                bool programmatic) {
   const long long items = (long long)n_listed * (p->feat_len / (4 * G));
   const long long grid = (items + 256 / G - 1) / (256 / G);
-  spmm_light_kernel<G, U, MSG, RED><<<(unsigned)grid, 256, 0, st>>>(
-      indptr, indices, vals, x, y, p->rows_dev + first, n_listed, items, p->feat_len);
+  return launch_kernel(spmm_light_kernel<G, U, MSG, RED>, (unsigned)grid, 256, 0, st, programmatic,
+                       indptr, indices, vals, x, y, p->rows_dev + first, n_listed, items,
+                       p->feat_len);
 }
 
 template <class Shape, int MSG, int RED>
 static cudaError_t launch_chain(const fg_spmm_plan* p, const int32_t* indptr,
                                 const int32_t* indices, const float* vals, const float* x,
-                                const OutPtrs& y, int first, int n_listed, cudaStream_t st) {
+                                const OutPtrs& y, int first, int n_listed, cudaStream_t st,
+                                bool programmatic) {
   const cudaError_t e =
       ensure_smem<spmm_chain_kernel<Shape, MSG, RED>>(Shape::SMEM_BYTES, p->device);
   if (e != cudaSuccess) return e;
   // one CTA per (row, 32-float slab)
   const unsigned grid = (unsigned)(n_listed * (p->feat_len / 32));
-  spmm_chain_kernel<Shape, MSG, RED><<<grid, 32 * Shape::WARPS, Shape::SMEM_BYTES, st>>>(
-      indptr, indices, vals, x, y, p->rows_dev + first, n_listed, p->slab_w / 32, p->feat_len,
-      p->status_dev, p->poll_limit);
-  return cudaGetLastError();
+  return launch_kernel(spmm_chain_kernel<Shape, MSG, RED>, grid, 32 * Shape::WARPS,
+                       Shape::SMEM_BYTES, st, programmatic, indptr, indices, vals, x, y,
+                       p->rows_dev + first, n_listed, p->slab_w / 32, p->feat_len, p->status_dev,
+                       p->poll_limit);
 }
 
 template <int VEC, int MSG, int RED>
 static cudaError_t launch_heavy(const fg_spmm_plan* p, const int32_t* indptr,
                                 const int32_t* indices, const float* vals, const float* x,
-                                const OutPtrs& y, cudaStream_t st) {
+                                const OutPtrs& y, cudaStream_t st, bool programmatic) {
   const cudaError_t e =
       ensure_smem<spmm_heavy_kernel<VEC, MSG, RED>>(heavy_smem_bytes<VEC>(), p->device);
   if (e != cudaSuccess) return e;
   const int slab = 32 * VEC;
   const long long items = (long long)p->n_heavy * (p->feat_len / slab);  // < INT32_MAX (plan)
-  spmm_heavy_kernel<VEC, MSG, RED><<<(unsigned)items, 32, heavy_smem_bytes<VEC>(), st>>>(
-      indptr, indices, vals, x, y, p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab,
-      p->feat_len);
-  return cudaGetLastError();
+  return launch_kernel(spmm_heavy_kernel<VEC, MSG, RED>, (unsigned)items, 32,
+                       heavy_smem_bytes<VEC>(), st, programmatic, indptr, indices, vals, x, y,
+                       p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab, p->feat_len);
 }
 
 // All kernels of one call for one operator pair.
@@ -1068,52 +1089,42 @@ static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const i
     return FG_OK;
   }
 
-  // Fork: giant and heavy rows run on the plan's own high-priority streams, the
-  // longest first, while the light kernel fills the rest of the machine; the
-  // caller's stream joins both before the call returns control to it -- also when a
-  // later launch fails, so that no kernel of this call is left writing Y unobserved.
-  if (p->fork_ev) FG_CUDA_TRY(cudaEventRecord(p->fork_ev, st));
-  bool giant_forked = false, heavy_forked = false;
-  auto launch_all = [&]() -> int {
-    if (p->n_giant > 0) {
-      FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_giant, p->fork_ev, 0));
-      giant_forked = true;
-      FG_CUDA_TRY((launch_chain<GiantShape, MSG, RED>(p, indptr, indices, vals, x, y, 0,
-                                                      p->n_giant, p->aux_giant)));
+  auto light = [&](cudaStream_t stream, bool programmatic) -> cudaError_t {
+    const int first = p->n_giant + p->n_heavy;
+    switch (p->slab_w) {
+      case 128: return launch_light<32, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, stream, programmatic);
+      case 64: return launch_light<16, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, stream, programmatic);
+      default: return launch_light<8, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, stream, programmatic);
     }
-    if (p->n_heavy > 0) {
-      FG_CUDA_TRY(cudaStreamWaitEvent(p->aux_heavy, p->fork_ev, 0));
-      heavy_forked = true;
-      if (p->heavy_vec == 2)
-        FG_CUDA_TRY((launch_heavy<2, MSG, RED>(p, indptr, indices, vals, x, y, p->aux_heavy)));
-      else
-        FG_CUDA_TRY((launch_heavy<1, MSG, RED>(p, indptr, indices, vals, x, y, p->aux_heavy)));
-    }
-    if (p->n_light > 0) {
-      const int first = p->n_giant + p->n_heavy;
-      switch (p->slab_w) {
-        case 128: launch_light<32, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, st); break;
-        case 64: launch_light<16, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, st); break;
-        default: launch_light<8, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, st); break;
-      }
-      FG_CUDA_TRY(cudaGetLastError());
-    }
-    return FG_OK;
   };
-  const int rc = launch_all();
-  cudaError_t join_err = cudaSuccess;
-  if (giant_forked) {
-    join_err = cudaEventRecord(p->join_giant, p->aux_giant);
-    if (join_err == cudaSuccess) join_err = cudaStreamWaitEvent(st, p->join_giant, 0);
+  auto heavy = [&](cudaStream_t stream, bool programmatic) -> cudaError_t {
+    return p->heavy_vec == 2
+               ? launch_heavy<2, MSG, RED>(p, indptr, indices, vals, x, y, stream, programmatic)
+               : launch_heavy<1, MSG, RED>(p, indptr, indices, vals, x, y, stream, programmatic);
+  };
+
+  // One stream, longest rows first: giant kernel, heavy kernel, light kernel, each
+  // dispatched as soon as every CTA of the one before it is resident (programmatic
+  // dependent launch) -- not when it has completed; the three write disjoint rows.  A
+  // giant CTA needs a whole SM, so it must get there before the light kernel's CTAs do:
+  // once they are on an SM the block scheduler keeps backfilling it with them and the
+  // giant rows, the call's critical path, start when the light kernel is nearly done.
+  // (Measured with the three kernels on three streams and fork / join events instead:
+  // 2.02 or 2.45 ms per call, depending on which launch reached the GPU first; this
+  // way 1.875 ms, every time.)  The last CTA of the heavy and of the light kernel waits
+  // for the grids before it, so whatever follows in the stream sees the whole SpMM
+  // complete.
+  bool any = false;
+  if (p->n_giant > 0) {
+    FG_CUDA_TRY((launch_chain<GiantShape, MSG, RED>(p, indptr, indices, vals, x, y, 0, p->n_giant,
+                                                    st, false)));
+    any = true;
   }
-  if (heavy_forked) {
-    cudaError_t e = cudaEventRecord(p->join_heavy, p->aux_heavy);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(st, p->join_heavy, 0);
-    if (join_err == cudaSuccess) join_err = e;
+  if (p->n_heavy > 0) {
+    FG_CUDA_TRY(heavy(st, any));
+    any = true;
   }
-  if (rc != FG_OK) return rc;
-  if (join_err != cudaSuccess)
-    return fail(FG_ERR_CUDA, "joining the plan's streams failed: %s", cudaGetErrorString(join_err));
+  if (p->n_light > 0) FG_CUDA_TRY(light(st, any));
   return FG_OK;
 }
 

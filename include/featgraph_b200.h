@@ -56,11 +56,10 @@ const char* fg_version(void);
 /* Opaque launch plan of one CSR matrix: the rows sorted by degree and cut into
  * three classes (light rows served by sub-warp groups, heavy rows by staged
  * single-warp CTAs, the few giant rows by producer/consumer CTAs), the
- * feature-slab width chosen from the device's L2 size, and two auxiliary
- * streams with their fork/join events on which the heavy and the giant kernel
- * run beside the light one.  Those streams and events are shared by every call
- * that uses the plan: one call in flight per plan (calls on one stream are
- * fine; two host threads or two streams using one plan at once race). */
+ * feature-slab width chosen from the device's L2 size, and the status word of
+ * the giant-row kernel's bounded waits.  A call launches its (up to three)
+ * kernels back to back on the caller's stream; the plan is read-only during a
+ * call apart from that status word, which all calls of one plan share. */
 typedef struct fg_spmm_plan fg_spmm_plan;
 
 /* Builds the plan from the HOST copy of indptr (n_rows + 1 int32 entries).

@@ -275,3 +275,23 @@ def test_partitioned_edges_and_edge_mapping(oracle, parts, shape):
     dup = sp.coo_matrix((np.ones(3, np.float32), ([1, 1, 2], [3, 3, 0])), shape=(230, 190))
     with pytest.raises(ValueError, match="duplicate-free"):
         PartitionedSDDMMcuda(dup, num_col_partitions=2)
+
+
+def test_multi_head_results_reach_an_unaligned_output(oracle):
+    # with H a multiple of four a lane stores its heads four at a time (16 bytes); an output
+    # that is not 16-byte aligned must take the 4-byte stores instead
+    import ctypes
+    coo = random_csr(170, 140, 0.1, seed=71).tocoo()
+    src, dst = features((140, 8, 8), seed=72), features((170, 8, 8), seed=73)
+    want = oracle.sddmm_coo_f32(coo.row, coo.col, src, dst, num_heads=8)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    r, c, s, d = dev(coo.row), dev(coo.col), dev(src), dev(dst)
+    buf = torch.full((coo.nnz * 8 + 1,), float("nan"), device="cuda")
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    for off in (0, 1):
+        out = buf[off:off + coo.nnz * 8]
+        assert out.data_ptr() % 16 == 4 * off
+        _lib.check(_lib.load().fg_sddmm_coo_f32(vp(r), vp(c), vp(s), vp(d), vp(out), coo.nnz, 170,
+                                                140, 64, 8, 0, None))
+        torch.cuda.synchronize()
+        assert np.array_equal(bits(want).reshape(-1), bits(out.cpu().numpy()))

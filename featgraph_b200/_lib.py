@@ -32,9 +32,10 @@ EXPORTED_SYMBOLS = (
     "fg_sddmm_coo_f32", "fg_sddmm_coo_f32_host", "fg_sddmm_num_launches", "fg_sddmm_describe",
     "fg_shard_rows_by_nnz", "fg_shard_edges",
     "fg_spmm_csr_f32_mcast", "fg_sddmm_coo_f32_mcast", "fg_peer_barrier", "fg_gather_probe",
-    "fg_spmm_csr_f32_general", "fg_sddmm_coo_f32_general",
+    "fg_spmm_csr_f32_general", "fg_sddmm_coo_f32_general", "fg_next_launch_options",
 )
 
+LAUNCH_PROGRAMMATIC, SPMM_GIANT_ROWS_ONLY, SPMM_SKIP_GIANT_ROWS = 1, 2, 4     # enum fg_launch_flags
 MSG_OPS = ("mul", "add", "sub", "div", "copy_lhs", "copy_rhs")    # enum fg_msg_op
 REDUCE_OPS = ("sum", "max", "min")                                # enum fg_reduce_op
 
@@ -58,6 +59,7 @@ def load():
     lib.fg_spmm_plan_num_launches.argtypes = [c_void]
     lib.fg_spmm_plan_status.argtypes = [c_void, c_i32p]
     lib.fg_spmm_plan_set_poll_limit.argtypes = [c_void, i64]
+    lib.fg_next_launch_options.argtypes = [i32, i32]
     lib.fg_spmm_csr_f32.argtypes = [c_void] * 7
     lib.fg_spmm_csr_f32_host.argtypes = [c_void] * 9
     lib.fg_spmm_csr_f32_multi.argtypes = [c_void] * 5 + [ctypes.POINTER(c_void), i32, c_void]

@@ -20,7 +20,26 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+static thread_local LaunchOptions g_next_options;
+
+LaunchOptions take_launch_options() {
+  const LaunchOptions o = g_next_options;
+  g_next_options = LaunchOptions();
+  return o;
+}
+
 }  // namespace fg
+
+extern "C" int fg_next_launch_options(int32_t flags, int32_t max_ctas) {
+  const int32_t known = FG_LAUNCH_PROGRAMMATIC | FG_SPMM_GIANT_ROWS_ONLY | FG_SPMM_SKIP_GIANT_ROWS;
+  if ((flags & ~known) != 0 || max_ctas < 0 ||
+      ((flags & FG_SPMM_GIANT_ROWS_ONLY) && (flags & FG_SPMM_SKIP_GIANT_ROWS)))
+    return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad launch options: flags=%d max_ctas=%d", (int)flags,
+                    (int)max_ctas);
+  fg::g_next_options.flags = flags;
+  fg::g_next_options.max_ctas = max_ctas;
+  return FG_OK;
+}
 
 extern "C" const char* fg_last_error_string(void) { return fg::last_error().c_str(); }
 

@@ -49,6 +49,13 @@ constexpr unsigned kPeerBarrierPolls = 1u << 22;
     case 15: CALL(5, 0); break;  case 16: CALL(5, 1); break;  default: CALL(5, 2); break;  \
   }
 
+// Options of the next kernel-launching call of the calling host thread (fg_next_launch_options).
+struct LaunchOptions {
+  int flags = 0;
+  int max_ctas = 0;
+};
+LaunchOptions take_launch_options();  // returns them and resets them to none
+
 // ---- host side: per-thread error message -----------------------------------
 std::string& last_error();
 int fail(int code, const char* fmt, ...);

@@ -55,12 +55,14 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
                   int tiles_per_warp, int vec_heads) {
   constexpr unsigned kFull = 0xffffffffu;
   extern __shared__ __align__(16) float smem[];
+  launch_dependents();  // a kernel launched programmatically behind this one may be dispatched
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   float* wbuf = smem + warp * kSdWarpFloats;
 
   const long long n_tiles = (nnz + 31) / 32;
   const long long tile0 = ((long long)blockIdx.x * kSdWarps + warp) * tiles_per_warp;
+  // (warp 0 of every CTA has tiles, so the wait at the end of the last CTA is always reached)
   if (tile0 >= n_tiles) return;
   const int my_tiles = (int)min((long long)tiles_per_warp, n_tiles - tile0);
   const int n_chunks = F / kSdChunk;
@@ -206,6 +208,10 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
     __syncwarp();  // every lane is done with this buffer before it is refilled
   }
   cp_async_wait<0>();
+  // If this grid was dispatched behind another one without waiting for it (programmatic
+  // launch), its last CTA stays until that one has completed: "this grid is complete" then
+  // covers both for whatever follows in the stream.
+  if (blockIdx.x == gridDim.x - 1 && warp == 0) wait_for_prior_grids();
 }
 
 template <int MSG, int RED>
@@ -213,6 +219,8 @@ __global__ void __launch_bounds__(256)
 sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
                      const float* __restrict__ src, const float* __restrict__ dst,
                      const __grid_constant__ OutPtrs out, long long n_out, int F, int H) {
+  launch_dependents();
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) wait_for_prior_grids();  // thread 0 is valid
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= n_out) return;
   const long long e = i / H;
@@ -326,8 +334,25 @@ extern "C" int fg_sddmm_describe(int64_t nnz, int32_t feat_len, int32_t num_head
 
 namespace fg {
 
+template <typename... Params, typename... Args>
+static cudaError_t launch_kernel(void (*kernel)(Params...), unsigned grid, unsigned block,
+                                 size_t smem, cudaStream_t st, bool programmatic, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = programmatic ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 template <int MSG, int RED>
-static cudaError_t sddmm_launch_kernels(int variant, long long grid, const int32_t* row,
+static cudaError_t sddmm_launch_kernels(int variant, long long grid, int tiles_per_warp,
+                                        bool programmatic, const int32_t* row,
                                         const int32_t* col, const float* src, const float* dst,
                                         const OutPtrs& out, int64_t nnz, int32_t feat_len,
                                         int32_t num_heads, int32_t device, cudaStream_t st) {
@@ -335,11 +360,9 @@ static cudaError_t sddmm_launch_kernels(int variant, long long grid, const int32
   int vec_heads = num_heads % 4 == 0;
   for (int q = 0; q < out.n; ++q)
     if (reinterpret_cast<uintptr_t>(out.p[q]) % 16 != 0) vec_heads = 0;
-  if (variant < 0) {
-    sddmm_generic_kernel<MSG, RED><<<(unsigned)grid, 256, 0, st>>>(
-        row, col, src, dst, out, (long long)nnz * num_heads, feat_len, num_heads);
-    return cudaGetLastError();
-  }
+  if (variant < 0)
+    return launch_kernel(sddmm_generic_kernel<MSG, RED>, (unsigned)grid, 256, 0, st, programmatic,
+                         row, col, src, dst, out, (long long)nnz * num_heads, feat_len, num_heads);
 #define FG_SD_LAUNCH(HPC)                                                                     \
   do {                                                                                        \
     static thread_local int configured_dev = -1;                                              \
@@ -350,8 +373,11 @@ static cudaError_t sddmm_launch_kernels(int variant, long long grid, const int32
       if (e__ != cudaSuccess) return e__;                                                     \
       configured_dev = device;                                                                \
     }                                                                                         \
-    sddmm_tile_kernel<HPC, MSG, RED><<<(unsigned)grid, kSdWarps * 32, kSdSmemBytes, st>>>(    \
-        row, col, src, dst, out, nnz, feat_len, num_heads, kSdTilesPerWarp, vec_heads);       \
+    cudaError_t l__ = launch_kernel(sddmm_tile_kernel<HPC, MSG, RED>, (unsigned)grid,         \
+                                    kSdWarps * 32, kSdSmemBytes, st, programmatic, row, col,  \
+                                    src, dst, out, (long long)nnz, feat_len, num_heads,       \
+                                    tiles_per_warp, vec_heads);                               \
+    if (l__ != cudaSuccess) return l__;                                                       \
   } while (0)
   switch (variant) {
     case 0: FG_SD_LAUNCH(0); break;
@@ -372,6 +398,7 @@ static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src
                         int32_t num_heads, int32_t device, void* stream,
                         int32_t msg_op = FG_MSG_MUL, int32_t reduce_op = FG_REDUCE_SUM) {
   using namespace fg;
+  const LaunchOptions opt = take_launch_options();
   if (msg_op < FG_MSG_MUL || msg_op > FG_MSG_COPY_RHS || reduce_op < FG_REDUCE_SUM ||
       reduce_op > FG_REDUCE_MIN)
     return fail(FG_ERR_INVALID_ARGUMENT, "unknown msg_op %d or reduce_op %d", (int)msg_op,
@@ -405,19 +432,26 @@ static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src
                        (reinterpret_cast<uintptr_t>(dst) % 16 == 0);
   const int variant = aligned ? sddmm_variant(feat_len, num_heads) : -1;
   long long grid;
+  long long tiles_per_warp = kSdTilesPerWarp;
   if (variant < 0) {
     grid = ((long long)nnz * num_heads + 255) / 256;
     if (grid >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "output too large for the generic kernel");
   } else {
     const long long tiles = (nnz + 31) / 32;
-    const long long per_cta = (long long)kSdWarps * kSdTilesPerWarp;
+    // a bounded grid (max_ctas): every warp walks a longer stretch of the edge list
+    if (opt.max_ctas > 0)
+      tiles_per_warp = std::max<long long>(
+          tiles_per_warp, (tiles + (long long)kSdWarps * opt.max_ctas - 1) / ((long long)kSdWarps * opt.max_ctas));
+    if (tiles_per_warp >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "edge count too large");
+    const long long per_cta = (long long)kSdWarps * tiles_per_warp;
     grid = (tiles + per_cta - 1) / per_cta;
     if (grid >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "edge count too large");
   }
+  const bool programmatic = (opt.flags & FG_LAUNCH_PROGRAMMATIC) != 0;
   cudaError_t err = cudaSuccess;
 #define FG_SD_OPS(M, R)                                                                          \
-  err = sddmm_launch_kernels<M, R>(variant, grid, row, col, src, dst, out, nnz, feat_len,       \
-                                   num_heads, device, st)
+  err = sddmm_launch_kernels<M, R>(variant, grid, (int)tiles_per_warp, programmatic, row, col,  \
+                                   src, dst, out, nnz, feat_len, num_heads, device, st)
   FG_DISPATCH_OPS(msg_op, reduce_op, FG_SD_OPS);
 #undef FG_SD_OPS
   FG_CUDA_TRY(err);

@@ -53,6 +53,7 @@ spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
                   const __grid_constant__ OutPtrs Y, const int* __restrict__ rows, int n_listed,
                   long long n_items, int F) {
   constexpr unsigned kFull = 0xffffffffu;
+  launch_dependents();  // a kernel launched programmatically behind this one may be dispatched
   constexpr int T = G > U ? G : U;  // nonzeros per index / value tile: one per lane, or two
   constexpr int PER = T / G;        // index words per lane and tile
   const int gl = threadIdx.x % G;  // lane within the group
@@ -673,6 +674,7 @@ spmm_chain_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     return;
   }
   heavy_store_row<1>(Y, (size_t)row * F + (size_t)sub * 32, lane, acc, 0.f);
+  if (blockIdx.x == gridDim.x - 1) wait_for_prior_grids();  // as in spmm_light_kernel
 }
 
 // Fallback for any feat_len / alignment: one warp per row, lanes over features.
@@ -681,6 +683,7 @@ __global__ void __launch_bounds__(256)
 spmm_generic_kernel(const int* __restrict__ indptr, const int* __restrict__ indices,
                     const float* __restrict__ vals, const float* __restrict__ X,
                     const __grid_constant__ OutPtrs Y, long long n_rows, int F) {
+  launch_dependents();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= n_rows) return;
@@ -694,6 +697,7 @@ spmm_generic_kernel(const int* __restrict__ indptr, const int* __restrict__ indi
       out_store(Y, (size_t)row * F + f, acc);
     }
   }
+  if (blockIdx.x == gridDim.x - 1) wait_for_prior_grids();  // as in spmm_light_kernel
 }
 
 }  // namespace fg
@@ -1080,12 +1084,17 @@ static cudaError_t launch_heavy(const fg_spmm_plan* p, const int32_t* indptr,
 template <int MSG, int RED>
 static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
                            const float* vals, const float* x, const OutPtrs& y, bool aligned,
-                           cudaStream_t st) {
-  if (!p->vector_ok || !aligned) {
+                           cudaStream_t st, const LaunchOptions& opt) {
+  // `any`: the next launch of this call may be programmatic -- because the call itself is
+  // (the caller's assertion), or because a kernel of this call is already in the stream
+  bool any = (opt.flags & FG_LAUNCH_PROGRAMMATIC) != 0;
+  const bool giants = (opt.flags & FG_SPMM_SKIP_GIANT_ROWS) == 0;
+  const bool rest = (opt.flags & FG_SPMM_GIANT_ROWS_ONLY) == 0;
+  if (!p->vector_ok || !aligned) {  // no row classes here: the whole SpMM is "the rest"
+    if (!rest) return FG_OK;
     const long long grid = (p->n_rows + 7) / 8;
-    spmm_generic_kernel<MSG, RED><<<(unsigned)grid, 256, 0, st>>>(indptr, indices, vals, x, y,
-                                                                  p->n_rows, p->feat_len);
-    FG_CUDA_TRY(cudaGetLastError());
+    FG_CUDA_TRY(launch_kernel(spmm_generic_kernel<MSG, RED>, (unsigned)grid, 256, 0, st, any, indptr,
+                              indices, vals, x, y, (long long)p->n_rows, p->feat_len));
     return FG_OK;
   }
 
@@ -1114,12 +1123,12 @@ static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const i
   // way 1.875 ms, every time.)  The last CTA of the heavy and of the light kernel waits
   // for the grids before it, so whatever follows in the stream sees the whole SpMM
   // complete.
-  bool any = false;
-  if (p->n_giant > 0) {
+  if (giants && p->n_giant > 0) {
     FG_CUDA_TRY((launch_chain<GiantShape, MSG, RED>(p, indptr, indices, vals, x, y, 0, p->n_giant,
-                                                    st, false)));
+                                                    st, any)));
     any = true;
   }
+  if (!rest) return FG_OK;
   if (p->n_heavy > 0) {
     FG_CUDA_TRY(heavy(st, any));
     any = true;
@@ -1135,6 +1144,7 @@ static int spmm_launch(const fg_spmm_plan* p, const int32_t* indptr, const int32
                        int mcast, void* stream, int32_t msg_op = FG_MSG_MUL,
                        int32_t reduce_op = FG_REDUCE_SUM) {
   using namespace fg;
+  const LaunchOptions opt = take_launch_options();
   if (!p) return fail(FG_ERR_INVALID_ARGUMENT, "plan is null");
   if (!ys || n_ys < 1 || n_ys > kMaxOutputs)
     return fail(FG_ERR_INVALID_ARGUMENT, "need 1 to %d output pointers, got %d", kMaxOutputs,
@@ -1162,7 +1172,8 @@ static int spmm_launch(const fg_spmm_plan* p, const int32_t* indptr, const int32
     return fail(FG_ERR_CUDA, "cannot select device %d: %s", p->device,
                 cudaGetErrorString(guard.status));
   int rc = FG_OK;
-#define FG_SPMM_OPS(M, R) rc = spmm_launch_ops<M, R>(p, indptr, indices, vals, x, y, aligned, st)
+#define FG_SPMM_OPS(M, R) \
+  rc = spmm_launch_ops<M, R>(p, indptr, indices, vals, x, y, aligned, st, opt)
   FG_DISPATCH_OPS(msg_op, reduce_op, FG_SPMM_OPS);
 #undef FG_SPMM_OPS
   return rc;

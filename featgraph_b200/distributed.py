@@ -443,50 +443,42 @@ class ShardedSDDMM(_Sharded):
 
 
 class OverlappedPair(object):
-    """One SpMM and one SDDMM that do not depend on each other, issued side by side.
+    """One SpMM and one SDDMM that do not depend on each other, run as one chain.
 
-    On a shard the SpMM is bound by the dependent add chain of its longest row (a handful of
-    CTAs for hundreds of microseconds) and the SDDMM by moving its results to the peers, so
-    the two leave each other's resource idle; here the SDDMM runs on a second stream beside
-    the SpMM and the pair shares ONE barrier before and ONE after instead of two each.
+    On a shard the SpMM is bound by the dependent add chain of its longest row: a handful of
+    whole-SM CTAs run for hundreds of microseconds after the rest of the SpMM is done, and
+    the SMs idle.  Here the SDDMM is launched programmatically behind the SpMM in the SAME
+    stream (fg_next_launch_options): it is dispatched as soon as the SpMM's last kernel is
+    resident and fills the machine under the giant rows' tail; and the pair shares ONE
+    barrier before and ONE after instead of two each.  Measured on 4 GPUs (feat_len 64, ms
+    per step): one after the other 1.48, this chain 1.37.  What was tried and dropped: the
+    SDDMM on a second stream beside the SpMM -- its CTAs take every SM first and the giant
+    rows, which need a whole SM each, start when it has drained (1.46); the SDDMM between
+    the SpMM's giant rows and its other rows (1.43); the same with the SDDMM's grid bounded
+    so that both are resident at once (1.65 to 1.97: the SDDMM needs its full occupancy).
     """
 
     def __init__(self, spmm, sddmm):
         self.spmm, self.sddmm = spmm, sddmm
         self.device = spmm.device
-        self.side = torch.cuda.Stream(device=self.device)
         self.fused = spmm._symm is not None and sddmm._symm is not None
+        self.chained = self.device.type == "cuda" and hasattr(spmm, "module") \
+            and hasattr(sddmm, "module")
 
-    def run(self, x, src, dst, marks=None):
-        """Returns (spmm.out, sddmm.out), whole and identical on every rank.  ``marks``: an
-        optional list that receives four CUDA events -- SpMM start / end on the main stream,
-        SDDMM start / end on the side stream -- for per-kernel timing."""
+    def run(self, x, src, dst):
+        """Returns (spmm.out, sddmm.out), whole and identical on every rank."""
         spmm, sddmm = self.spmm, self.sddmm
-        main = torch.cuda.current_stream(self.device)
         if self.fused:
             spmm._sync.barrier()
-        self.side.wait_stream(main)
-        if marks is not None:
-            marks.append(_record(main))
         spmm.launch_local(x)
-        if marks is not None:
-            marks.append(_record(main))
-        with torch.cuda.stream(self.side):
-            if marks is not None:
-                marks.append(_record(self.side))
-            sddmm.launch_local(src, dst)
-            if marks is not None:
-                marks.append(_record(self.side))
-        main.wait_stream(self.side)
+        if sddmm.edge_hi > sddmm.edge_lo:
+            if self.chained:
+                sddmm.module.run([src, dst], launch_flags=_lib.LAUNCH_PROGRAMMATIC)
+            else:
+                sddmm.launch_local(src, dst)
         if self.fused:
             spmm._sync.barrier()
         elif spmm.world > 1:
             spmm.gather()
             sddmm.gather()
         return spmm.out, sddmm.out
-
-
-def _record(stream):
-    ev = torch.cuda.Event(enable_timing=True)
-    ev.record(stream)
-    return ev

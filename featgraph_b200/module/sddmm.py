@@ -123,7 +123,10 @@ class SDDMMbase(object):
         self._mcast_output = int(mcast_pointer) if mcast_pointer else None
         self._extra_outputs = None
 
-    def _launch(self, src, dst):
+    def _launch(self, src, dst, flags=0, max_ctas=0):
+        """``flags`` / ``max_ctas``: fg_next_launch_options for this one call."""
+        if flags or max_ctas:
+            _lib.check(_lib.load().fg_next_launch_options(int(flags), int(max_ctas)))
         a = self._spec.attrs
         if (a["msg_op"], a["reduce_op"]) != ("mul", "sum"):
             if getattr(self, "_mcast_output", None) or getattr(self, "_extra_outputs", None):
@@ -180,11 +183,12 @@ class SDDMMbase(object):
         dst = as_device_tensor(input_tvm_ndarrays[1], self._ctx, dp.shape, dp.dtype, "DstFeat")
         return src, dst
 
-    def run(self, input_tvm_ndarrays):
+    def run(self, input_tvm_ndarrays, launch_flags=0, max_ctas=0):
         """Launch with [SrcFeat (indexed by col), DstFeat (indexed by row)]; returns
-        ``self.out_tvm``, the same array every call (sddmm.py:115-129)."""
+        ``self.out_tvm``, the same array every call (sddmm.py:115-129).  ``launch_flags`` /
+        ``max_ctas`` (additions): fg_next_launch_options for this call."""
         src, dst = self._checked_inputs(input_tvm_ndarrays)
-        self._launch(src, dst)
+        self._launch(src, dst, launch_flags, max_ctas)
         return self.out_tvm
 
     def measure_average_time(self, input_tvm_ndarrays, num_runs):

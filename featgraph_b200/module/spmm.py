@@ -147,7 +147,11 @@ class SpMMbase(object):
         self._mcast_output = int(mcast_pointer) if mcast_pointer else None
         self._extra_outputs = None
 
-    def _launch(self, x):
+    def _launch(self, x, flags=0):
+        """``flags``: fg_launch_flags for this one call (giant rows only / all but them /
+        programmatic first kernel); see fg_next_launch_options."""
+        if flags:
+            _lib.check(_lib.load().fg_next_launch_options(int(flags), 0))
         a = self._spec.attrs
         if (a["msg_op"], a["reduce_op"]) != ("mul", "sum"):
             if getattr(self, "_mcast_output", None) or getattr(self, "_extra_outputs", None):
@@ -187,11 +191,13 @@ class SpMMbase(object):
         src = self._spec.inputs[0]
         return as_device_tensor(input_tvm_ndarrays[0], self._ctx, src.shape, src.dtype, "SrcFeat")
 
-    def run(self, input_tvm_ndarrays):
+    def run(self, input_tvm_ndarrays, launch_flags=0):
         """Launch on the current stream of the module's device; returns ``self.out_tvm``,
-        the same array every call (spmm.py:142-161).  Asynchronous until it is read."""
+        the same array every call (spmm.py:142-161).  Asynchronous until it is read.
+        ``launch_flags`` (an addition): fg_launch_flags, for callers that interleave the
+        SpMM's phases with another kernel (featgraph_b200.distributed.OverlappedPair)."""
         x = self._checked_input(input_tvm_ndarrays)
-        self._launch(x)
+        self._launch(x, launch_flags)
         return self.out_tvm
 
     def measure_average_time(self, input_tvm_ndarrays, num_runs):

@@ -51,6 +51,34 @@ const char* fg_last_error_string(void);
 /* Library version, "major.minor.patch". */
 const char* fg_version(void);
 
+/* Options for the NEXT fg_spmm_csr_f32* / fg_sddmm_coo_f32* call of the calling host
+ * thread; that call consumes them.  They let a caller put an SpMM and an SDDMM that do
+ * not depend on each other into one stream so that the second fills the machine under
+ * the tail of the first (the SpMM's giant rows: a few whole-SM CTAs that outlast the rest):
+ *     fg_spmm_csr_f32(...);
+ *     fg_next_launch_options(FG_LAUNCH_PROGRAMMATIC, 0);     fg_sddmm_coo_f32(...);
+ * or, with the SpMM cut in two around the SDDMM:
+ *     fg_next_launch_options(FG_SPMM_GIANT_ROWS_ONLY, 0);            fg_spmm_csr_f32(...);
+ *     fg_next_launch_options(FG_LAUNCH_PROGRAMMATIC, 0);             fg_sddmm_coo_f32(...);
+ *     fg_next_launch_options(FG_SPMM_SKIP_GIANT_ROWS | FG_LAUNCH_PROGRAMMATIC, 0);
+ *                                                                    fg_spmm_csr_f32(...);
+ * FG_LAUNCH_PROGRAMMATIC: the call's first kernel may be dispatched as soon as every CTA
+ *   of the kernel before it in the stream is resident, instead of when that kernel has
+ *   completed (programmatic dependent launch).  The caller asserts that this call reads
+ *   nothing that kernel writes.  The last CTA of each of this library's kernels waits
+ *   for the grid before it, so a later, ordinary launch still sees all of them complete.
+ * FG_SPMM_GIANT_ROWS_ONLY / FG_SPMM_SKIP_GIANT_ROWS: the SpMM call computes only the
+ *   plan's giant rows / everything but them; the two calls together are one SpMM.
+ * max_ctas > 0 (SDDMM): at most this many CTAs, each walking more edges, so that the whole
+ *   grid is resident at once and the kernel behind it can be dispatched beside it.
+ * The reference has no counterpart (one kernel, one stream). */
+enum fg_launch_flags {
+  FG_LAUNCH_PROGRAMMATIC = 1,
+  FG_SPMM_GIANT_ROWS_ONLY = 2,
+  FG_SPMM_SKIP_GIANT_ROWS = 4
+};
+int fg_next_launch_options(int32_t flags, int32_t max_ctas);
+
 /* ------------------------------------------------------------------ SpMM -- */
 
 /* Opaque launch plan of one CSR matrix: the rows sorted by degree and cut into

@@ -79,7 +79,8 @@ def _worker(rank, world, port):
                                       bits(out.cpu().numpy())), \
                     "rank %d SDDMM %r (%s)" % (rank, shape, sd.gather_mode)
                 assert sd.device_status() == 0
-            # the two operators side by side on two streams, one barrier pair around both
+            # the two operators side by side in one chain of programmatic launches, one
+            # barrier pair around both
             out.zero_()
             y.zero_()
             pair = OverlappedPair(spmm, sd)

@@ -33,6 +33,8 @@ EXPORTED_SYMBOLS = (
     "fg_shard_rows_by_nnz", "fg_shard_edges",
     "fg_spmm_csr_f32_mcast", "fg_sddmm_coo_f32_mcast", "fg_peer_barrier", "fg_gather_probe",
     "fg_spmm_csr_f32_general", "fg_sddmm_coo_f32_general", "fg_next_launch_options",
+    "fg_spmm_dds_plan_create", "fg_spmm_dds_plan_destroy", "fg_spmm_dds_plan_num_launches",
+    "fg_spmm_dds_plan_status", "fg_spmm_dds_f32",
 )
 
 LAUNCH_PROGRAMMATIC, SPMM_GIANT_ROWS_ONLY, SPMM_SKIP_GIANT_ROWS = 1, 2, 4     # enum fg_launch_flags
@@ -60,6 +62,11 @@ def load():
     lib.fg_spmm_plan_status.argtypes = [c_void, c_i32p]
     lib.fg_spmm_plan_set_poll_limit.argtypes = [c_void, i64]
     lib.fg_next_launch_options.argtypes = [i32, i32]
+    lib.fg_spmm_dds_plan_create.argtypes = [c_i32p, i64, i64, i32, i32, i32, ctypes.POINTER(c_void)]
+    lib.fg_spmm_dds_plan_destroy.argtypes = [c_void]
+    lib.fg_spmm_dds_plan_num_launches.argtypes = [c_void]
+    lib.fg_spmm_dds_plan_status.argtypes = [c_void, c_i32p]
+    lib.fg_spmm_dds_f32.argtypes = [c_void] * 7
     lib.fg_spmm_csr_f32.argtypes = [c_void] * 7
     lib.fg_spmm_csr_f32_host.argtypes = [c_void] * 9
     lib.fg_spmm_csr_f32_multi.argtypes = [c_void] * 5 + [ctypes.POINTER(c_void), i32, c_void]

@@ -58,6 +58,26 @@ def _load_graph(args, device):
     return g, "synthetic:" + args.synthetic
 
 
+class _PartitionedSpMM(object):
+    """The DDS form of the SpMM (VanillaSpMMcuda with num_col_partitions > 1) behind the
+    few names the timing loop uses."""
+    gather_mode = "none"
+
+    def __init__(self, adj, feat_len, device_id, parts):
+        from . import te
+        from .module import VanillaSpMMcuda
+        self.module = VanillaSpMMcuda(adj, device_id=device_id, num_col_partitions=parts)
+        self.module.build([te.placeholder((adj.shape[1], feat_len))], {}, {})
+        self.out = None
+
+    def run(self, x):
+        self.out = self.module.run([x]).torch
+        return self.out
+
+    def device_status(self):
+        return self.module.device_status()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--kernel", choices=["spmm", "sddmm"], default="spmm")
@@ -75,7 +95,9 @@ def main(argv=None):
     ap.add_argument("--scale", type=int, default=24, help="R-MAT scale (2**scale vertices)")
     ap.add_argument("--row-partitions", type=int, default=1,
                     help="SDDMM: the reference's 2-D edge blocking (VanillaSDDMMx86's arguments)")
-    ap.add_argument("--col-partitions", type=int, default=1)
+    ap.add_argument("--col-partitions", type=int, default=1,
+                    help="SpMM (one GPU): the reference's 1-D source-vertex partitioning, "
+                         "VanillaSpMMx86's num_col_partitions; SDDMM: see --row-partitions")
     ap.add_argument("--sweep", action="store_true",
                     help="run the whole configured sweep in one process: SpMM and SDDMM at feat-len "
                          "32 ... 512, then multi-head SDDMM (4,16), (8,32), (16,64)")
@@ -133,7 +155,12 @@ def main(argv=None):
         x = graphs.normal_features(g.n_cols, shape, graphs.FEAT_SEED, device)
         if kernel == "spmm":
             nnz = g.nnz
-            op = ShardedSpMM(adj, f, device, peer_mode=args.peer_mode)
+            if args.col_partitions > 1:
+                if world > 1:
+                    raise SystemExit("--col-partitions with --kernel spmm runs on one GPU")
+                op = _PartitionedSpMM(adj, f, local, args.col_partitions)
+            else:
+                op = ShardedSpMM(adj, f, device, peer_mode=args.peer_mode)
             call = lambda: op.run(x)                       # noqa: E731
             alg = 4 * (n + 1) + 8 * nnz + 4 * nnz * f + 4 * n * f
         else:

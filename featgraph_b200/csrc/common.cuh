@@ -27,8 +27,11 @@ namespace fg {
 constexpr int kMaxOutputs = 8;
 struct OutPtrs {
   float* p[kMaxOutputs];
-  int n;
-  int mcast;
+  int n = 0;
+  int mcast = 0;
+  // SpMM over column blocks only (out_fold): 0 store the result; 1 store 0 + result (the
+  // first block); 2 store what p[0] holds + result (every later block)
+  int accumulate = 0;
 };
 
 // The flag arrays of fg_peer_barrier, one per rank (peer-mapped pointers), and how long a
@@ -148,6 +151,24 @@ __device__ __forceinline__ void st_stream4(float* p, float4 v) {
 }
 
 // ---- result stores: every listed buffer, or one multicast store ---------------
+// The running sum over column blocks: the value to store for a result `v` at `off`.
+__device__ __forceinline__ float out_fold(const OutPtrs& o, size_t off, float v) {
+  if (o.accumulate == 0) return v;
+  return __fadd_rn(o.accumulate == 2 ? o.p[0][off] : 0.0f, v);
+}
+__device__ __forceinline__ float2 out_fold(const OutPtrs& o, size_t off, float2 v) {
+  if (o.accumulate == 0) return v;
+  float2 prev = make_float2(0.f, 0.f);
+  if (o.accumulate == 2) prev = *reinterpret_cast<const float2*>(o.p[0] + off);
+  return make_float2(__fadd_rn(prev.x, v.x), __fadd_rn(prev.y, v.y));
+}
+__device__ __forceinline__ float4 out_fold(const OutPtrs& o, size_t off, float4 v) {
+  if (o.accumulate == 0) return v;
+  float4 prev = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (o.accumulate == 2) prev = *reinterpret_cast<const float4*>(o.p[0] + off);
+  return make_float4(__fadd_rn(prev.x, v.x), __fadd_rn(prev.y, v.y), __fadd_rn(prev.z, v.z),
+                     __fadd_rn(prev.w, v.w));
+}
 __device__ __forceinline__ void out_store(const OutPtrs& o, size_t off, float v) {
   if (o.mcast) {
     asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(o.p[0] + off), "f"(v)

@@ -144,8 +144,10 @@ spmm_light_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
     }
     if (cnt > 0) e += (cnt < T ? cnt : T);
   }
-  if (valid)
-    out_store(Y, (size_t)row * F + col_off, make_float4(acc_lo.x, acc_lo.y, acc_hi.x, acc_hi.y));
+  if (valid) {
+    const size_t off = (size_t)row * F + col_off;
+    out_store(Y, off, out_fold(Y, off, make_float4(acc_lo.x, acc_lo.y, acc_hi.x, acc_hi.y)));
+  }
   // This grid may have been dispatched behind the heavy / giant kernels of the same call
   // without waiting for them; its last CTA stays until they have completed, so that "this
   // grid is complete" means "the whole SpMM is complete" to whatever follows in the stream.
@@ -201,9 +203,9 @@ template <int VEC>
 __device__ __forceinline__ void heavy_store_row(const OutPtrs& Y, size_t slab_off, int lane,
                                                 float acc_a, float acc_b) {
   if (VEC == 2)
-    out_store(Y, slab_off + lane * 2, make_float2(acc_a, acc_b));
+    out_store(Y, slab_off + lane * 2, out_fold(Y, slab_off + lane * 2, make_float2(acc_a, acc_b)));
   else
-    out_store(Y, slab_off + lane, acc_a);
+    out_store(Y, slab_off + lane, out_fold(Y, slab_off + lane, acc_a));
 }
 
 // Decodes blockIdx.x of the heavy / giant kernels: items are ordered
@@ -694,7 +696,7 @@ spmm_generic_kernel(const int* __restrict__ indptr, const int* __restrict__ indi
     if (f < F) {
       for (int e = beg; e < end; ++e)
         acc = combine<MSG, RED>(acc, X[(size_t)indices[e] * F + f], vals[e]);
-      out_store(Y, (size_t)row * F + f, acc);
+      out_store(Y, (size_t)row * F + f, out_fold(Y, (size_t)row * F + f, acc));
     }
   }
   if (blockIdx.x == gridDim.x - 1) wait_for_prior_grids();  // as in spmm_light_kernel
@@ -803,7 +805,6 @@ static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, in
   if (n_rows >= INT32_MAX || n_cols >= INT32_MAX)
     return fail(FG_ERR_UNSUPPORTED, "row/column counts must fit int32");
   if (!indptr) return fail(FG_ERR_INVALID_ARGUMENT, "indptr_host is null");
-  if (indptr[0] != 0) return fail(FG_ERR_INVALID_ARGUMENT, "indptr[0] must be 0");
   int64_t max_deg = 0;
   for (int64_t r = 0; r < n_rows; ++r) {
     const int64_t d = (int64_t)indptr[r + 1] - indptr[r];
@@ -816,7 +817,7 @@ static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, in
   p->device = device;
   p->n_rows = n_rows;
   p->n_cols = n_cols;
-  p->nnz = indptr[n_rows];
+  p->nnz = (int64_t)indptr[n_rows] - indptr[0];
   p->feat_len = feat_len;
   p->max_deg = max_deg;
   p->heavy_threshold = heavy_threshold > 0 ? heavy_threshold : kDefaultHeavyThreshold;
@@ -923,6 +924,7 @@ static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, in
 extern "C" int fg_spmm_plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols,
                                    int32_t feat_len, int32_t device, int32_t heavy_threshold,
                                    fg_spmm_plan** out_plan) {
+  if (indptr && indptr[0] != 0) return fg::fail(FG_ERR_INVALID_ARGUMENT, "indptr[0] must be 0");
   // the host-side containers may throw; the C ABI never does
   try {
     return fg::plan_create(indptr, n_rows, n_cols, feat_len, device, heavy_threshold, out_plan);
@@ -1142,7 +1144,7 @@ static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const i
 static int spmm_launch(const fg_spmm_plan* p, const int32_t* indptr, const int32_t* indices,
                        const float* vals, const float* x, float* const* ys, int32_t n_ys,
                        int mcast, void* stream, int32_t msg_op = FG_MSG_MUL,
-                       int32_t reduce_op = FG_REDUCE_SUM) {
+                       int32_t reduce_op = FG_REDUCE_SUM, int accumulate = 0) {
   using namespace fg;
   const LaunchOptions opt = take_launch_options();
   if (!p) return fail(FG_ERR_INVALID_ARGUMENT, "plan is null");
@@ -1157,6 +1159,7 @@ static int spmm_launch(const fg_spmm_plan* p, const int32_t* indptr, const int32
   OutPtrs y;
   y.n = n_ys;
   y.mcast = mcast;
+  y.accumulate = accumulate;
   bool aligned = reinterpret_cast<uintptr_t>(x) % 16 == 0;
   for (int q = 0; q < kMaxOutputs; ++q) {
     y.p[q] = q < n_ys ? ys[q] : nullptr;
@@ -1233,4 +1236,108 @@ extern "C" int fg_spmm_csr_f32_host(const fg_spmm_plan* p, const int32_t* indptr
   if (yb) FG_CUDA_TRY(cudaMemcpyAsync(y_host, y_stage, yb, cudaMemcpyDeviceToHost, st));
   FG_CUDA_TRY(cudaStreamSynchronize(st));
   return FG_OK;
+}
+
+// ------------------------------------------------- SpMM over column blocks (DDS) --
+//
+// The reference's 1-D source-vertex partitioning (vanilla_spmm_dds_x86,
+// python/featgraph/op/vanilla_spmm.py:149-246): the columns are cut into P blocks, block p
+// is a CSR matrix of its own over block-local column indices, and
+//   Out[row] = ((0 + S_0[row]) + S_1[row]) + ... ,   S_p[row] = the block's sum in stored order.
+// Here block p IS a CSR SpMM -- the same kernels, row pointers s1_pos + p * (n_rows + 1),
+// features X + p * width * feat_len -- whose stores add to the output instead of replacing
+// it (OutPtrs::accumulate).  The P calls follow each other in the stream, so block p + 1
+// gathers only from its own width * feat_len * 4 bytes of X: the partitioning's purpose,
+// features that stay in cache, with the 126 MB L2 in the role of the CPU's LLC.
+
+struct fg_spmm_dds_plan {
+  int device = 0, feat_len = 0, parts = 0;
+  int64_t n_rows = 0, n_cols = 0, width = 0;
+  std::vector<fg_spmm_plan*> blocks;
+};
+
+extern "C" int fg_spmm_dds_plan_destroy(fg_spmm_dds_plan* plan) {
+  if (!plan) return FG_OK;
+  for (fg_spmm_plan* b : plan->blocks) fg::plan_release(b);
+  delete plan;
+  return FG_OK;
+}
+
+extern "C" int fg_spmm_dds_plan_create(const int32_t* s1_pos, int64_t n_rows, int64_t n_cols,
+                                       int32_t feat_len, int32_t num_col_partitions,
+                                       int32_t device, fg_spmm_dds_plan** out_plan) {
+  using namespace fg;
+  if (!out_plan) return fail(FG_ERR_INVALID_ARGUMENT, "out_plan is null");
+  *out_plan = nullptr;
+  if (num_col_partitions < 1)
+    return fail(FG_ERR_INVALID_ARGUMENT, "num_col_partitions must be at least 1, got %d",
+                (int)num_col_partitions);
+  if (!s1_pos) return fail(FG_ERR_INVALID_ARGUMENT, "s1_pos_host is null");
+  if (n_rows < 0 || n_cols < 0) return fail(FG_ERR_INVALID_ARGUMENT, "bad shape");
+  if (s1_pos[0] != 0) return fail(FG_ERR_INVALID_ARGUMENT, "s1_pos[0] must be 0");
+  for (int64_t p = 1; p < num_col_partitions; ++p)
+    if (s1_pos[p * (n_rows + 1)] != s1_pos[p * (n_rows + 1) - 1])
+      return fail(FG_ERR_INVALID_ARGUMENT, "block %lld does not start where block %lld ends",
+                  (long long)p, (long long)p - 1);
+  try {
+    fg_spmm_dds_plan* d = new fg_spmm_dds_plan();
+    d->device = device;
+    d->feat_len = feat_len;
+    d->parts = num_col_partitions;
+    d->n_rows = n_rows;
+    d->n_cols = n_cols;
+    d->width = std::max<int64_t>((n_cols + num_col_partitions - 1) / num_col_partitions, 1);
+    for (int64_t p = 0; p < num_col_partitions; ++p) {
+      fg_spmm_plan* b = nullptr;
+      const int64_t cols = std::max<int64_t>(0, std::min(d->width, n_cols - p * d->width));
+      const int rc = plan_create(s1_pos + p * (n_rows + 1), n_rows, cols, feat_len, device, 0, &b);
+      if (rc != FG_OK) {
+        fg_spmm_dds_plan_destroy(d);
+        return rc;
+      }
+      d->blocks.push_back(b);
+    }
+    *out_plan = d;
+    return FG_OK;
+  } catch (const std::bad_alloc&) {
+    return fail(FG_ERR_OUT_OF_MEMORY, "fg_spmm_dds_plan_create: host allocation failed");
+  } catch (...) {
+    return fail(FG_ERR_CUDA, "fg_spmm_dds_plan_create: unexpected exception");
+  }
+}
+
+extern "C" int fg_spmm_dds_f32(const fg_spmm_dds_plan* d, const int32_t* s1_pos,
+                               const int32_t* s1_idx, const float* vals, const float* x,
+                               float* y, void* stream) {
+  using namespace fg;
+  take_launch_options();  // per-call options address the phases of one CSR call; none apply here
+  if (!d) return fail(FG_ERR_INVALID_ARGUMENT, "plan is null");
+  if (d->n_rows == 0) return FG_OK;
+  if (!s1_pos || !y) return fail(FG_ERR_INVALID_ARGUMENT, "s1_pos_dev or y_dev is null");
+  float* ys[1] = {y};
+  for (int64_t p = 0; p < d->parts; ++p) {
+    const int rc = spmm_launch(d->blocks[(size_t)p], s1_pos + p * (d->n_rows + 1), s1_idx, vals,
+                               x ? x + (size_t)p * d->width * d->feat_len : x, ys, 1, 0, stream,
+                               FG_MSG_MUL, FG_REDUCE_SUM, p == 0 ? 1 : 2);
+    if (rc != FG_OK) return rc;
+  }
+  return FG_OK;
+}
+
+extern "C" int fg_spmm_dds_plan_status(const fg_spmm_dds_plan* d, int32_t* device_status) {
+  using namespace fg;
+  if (!d || !device_status) return fail(FG_ERR_INVALID_ARGUMENT, "plan or device_status is null");
+  *device_status = 0;
+  for (const fg_spmm_plan* b : d->blocks) {
+    const int rc = fg_spmm_plan_status(b, device_status);
+    if (rc != FG_OK) return rc;
+  }
+  return FG_OK;
+}
+
+extern "C" int fg_spmm_dds_plan_num_launches(const fg_spmm_dds_plan* d) {
+  int n = 0;
+  if (d)
+    for (const fg_spmm_plan* b : d->blocks) n += fg_spmm_plan_num_launches(b);
+  return n;
 }

@@ -11,6 +11,7 @@ import torch
 
 from .. import _lib
 from ..op import vanilla_spmm_csr_cuda, schedule_vanilla_spmm_csr_cuda
+from ..op.vanilla_spmm import vanilla_spmm_dds_cuda, schedule_vanilla_spmm_dds_cuda
 from ..op.spec import no_x86
 from ..runtime import Placeholder, NDArray, array, cpu, gpu, zeros
 from ..util import util_convert_csr_to_dds
@@ -39,6 +40,21 @@ class SpMMbase(object):
             self._adj_s1_pos, self._adj_s1_idx, self._adj_vals = pos, idx, vals
             self._adj_d1_size = self._num_col_partitions
             self._adj_d2_size = self._num_rows + 1
+            if self._target == "cuda":
+                self._adj_s1_pos = self._index_array(pos, "s1_pos")
+                self._adj_s1_idx = self._index_array(idx, "s1_idx")
+                if vals.dtype != np.float32:
+                    raise TypeError("adjacency values must be float32 (got %s); cast the matrix "
+                                    "with .astype('float32') first" % vals.dtype)
+                self._adj_s1_pos_placeholder = Placeholder(self._adj_s1_pos.shape, "int32",
+                                                           "adj_s1_pos_placeholder")
+                self._adj_s1_idx_placeholder = Placeholder(self._adj_s1_idx.shape, "int32",
+                                                           "adj_s1_idx_placeholder")
+                self._adj_vals_placeholder = Placeholder(vals.shape, "float32",
+                                                         "adj_vals_placeholder")
+                self._adj_s1_pos_tvm = array(self._adj_s1_pos, self._ctx)
+                self._adj_s1_idx_tvm = array(self._adj_s1_idx, self._ctx)
+                self._adj_vals_tvm = array(np.ascontiguousarray(vals), self._ctx)
         else:
             self._adj_indptr = self._index_array(csr.indptr, "indptr")
             self._adj_indices = self._index_array(csr.indices, "indices")
@@ -78,11 +94,16 @@ class SpMMbase(object):
 
     # -- build ---------------------------------------------------------------------------
     def _specialise(self, input_placeholders, compute_args, schedule_args):
-        if self._target != "cuda" or self._num_col_partitions > 1:
+        if self._target != "cuda":
             raise no_x86(type(self).__name__ + ".build")
-        out = self._compute_func(*input_placeholders, self._adj_indptr_placeholder,
-                                 self._adj_indices_placeholder, self._adj_vals_placeholder,
-                                 **compute_args)
+        if self._num_col_partitions > 1:
+            out = self._compute_func(*input_placeholders, self._adj_s1_pos_placeholder,
+                                     self._adj_s1_idx_placeholder, self._adj_vals_placeholder,
+                                     self._adj_d1_size, self._adj_d2_size, **compute_args)
+        else:
+            out = self._compute_func(*input_placeholders, self._adj_indptr_placeholder,
+                                     self._adj_indices_placeholder, self._adj_vals_placeholder,
+                                     **compute_args)
         sched = self._schedule_func(out, **schedule_args)
         src = input_placeholders[0]
         if src.shape[0] != self._num_cols:
@@ -106,13 +127,8 @@ class SpMMbase(object):
         schedule_args = dict(schedule_args)
         threshold = int(schedule_args.pop("heavy_row_threshold", 0))
         out, sched = self._specialise(input_placeholders, compute_args, schedule_args)
-        lib = _lib.load()
         self._release_plan()
-        plan = ctypes.c_void_p()
-        _lib.check(lib.fg_spmm_plan_create(
-            self._adj_indptr.ctypes.data_as(_lib.c_i32p), self._num_rows, self._num_cols,
-            out.attrs["feat_len"], self._ctx.device_id, threshold, ctypes.byref(plan)))
-        self._plan, self._spec, self._func = plan, out, sched
+        self._plan, self._spec, self._func = self._make_plan(out, threshold), out, sched
         self.out_tvm = zeros(out.shape, out.dtype, self._ctx)
 
     def lower_to_ir(self, input_placeholders, compute_args, schedule_args):
@@ -122,16 +138,39 @@ class SpMMbase(object):
         threshold = int(schedule_args.pop("heavy_row_threshold", 0))
         out, sched = self._specialise(input_placeholders, compute_args, schedule_args)
         lib = _lib.load()
-        plan = ctypes.c_void_p()
-        _lib.check(lib.fg_spmm_plan_create(
-            self._adj_indptr.ctypes.data_as(_lib.c_i32p), self._num_rows, self._num_cols,
-            out.attrs["feat_len"], self._ctx.device_id, threshold, ctypes.byref(plan)))
+        plan = self._make_plan(out, threshold)
         try:
-            buf = ctypes.create_string_buffer(2048)
-            _lib.check(lib.fg_spmm_plan_describe(plan, buf, len(buf)))
+            if self._num_col_partitions > 1:
+                text = ("spmm_dds: %d column blocks of %d columns, one CSR plan each, %d kernel "
+                        "launches per call" % (self._num_col_partitions,
+                                               -(-self._num_cols // self._num_col_partitions),
+                                               lib.fg_spmm_dds_plan_num_launches(plan)))
+            else:
+                buf = ctypes.create_string_buffer(2048)
+                _lib.check(lib.fg_spmm_plan_describe(plan, buf, len(buf)))
+                text = buf.value.decode()
         finally:
-            lib.fg_spmm_plan_destroy(plan)
-        return buf.value.decode() + " | hints: %r" % (sched.hints,)
+            self._destroy(plan)
+        return text + " | hints: %r" % (sched.hints,)
+
+    def _make_plan(self, out, threshold):
+        lib = _lib.load()
+        plan = ctypes.c_void_p()
+        if self._num_col_partitions > 1:
+            _lib.check(lib.fg_spmm_dds_plan_create(
+                self._adj_s1_pos.ctypes.data_as(_lib.c_i32p), self._num_rows, self._num_cols,
+                out.attrs["feat_len"], self._num_col_partitions, self._ctx.device_id,
+                ctypes.byref(plan)))
+        else:
+            _lib.check(lib.fg_spmm_plan_create(
+                self._adj_indptr.ctypes.data_as(_lib.c_i32p), self._num_rows, self._num_cols,
+                out.attrs["feat_len"], self._ctx.device_id, threshold, ctypes.byref(plan)))
+        return plan
+
+    def _destroy(self, plan):
+        lib = _lib.load()
+        (lib.fg_spmm_dds_plan_destroy if self._num_col_partitions > 1
+         else lib.fg_spmm_plan_destroy)(plan)
 
     # -- run -----------------------------------------------------------------------------
     def set_extra_outputs(self, device_pointers):
@@ -150,6 +189,14 @@ class SpMMbase(object):
     def _launch(self, x, flags=0):
         """``flags``: fg_launch_flags for this one call (giant rows only / all but them /
         programmatic first kernel); see fg_next_launch_options."""
+        if self._num_col_partitions > 1:
+            if getattr(self, "_mcast_output", None) or getattr(self, "_extra_outputs", None):
+                raise NotImplementedError("extra outputs are provided for the CSR form only")
+            _lib.check(_lib.load().fg_spmm_dds_f32(
+                self._plan, ptr(self._adj_s1_pos_tvm.torch), ptr(self._adj_s1_idx_tvm.torch),
+                ptr(self._adj_vals_tvm.torch), ptr(x), ptr(self.out_tvm.torch),
+                current_stream_handle(self._ctx)))
+            return
         if flags:
             _lib.check(_lib.load().fg_next_launch_options(int(flags), 0))
         a = self._spec.attrs
@@ -212,6 +259,8 @@ class SpMMbase(object):
         the C ABI's fg_spmm_csr_f32_host with staging buffers owned by the module."""
         if self._plan is None:
             raise RuntimeError("build() must be called before run_host()")
+        if self._num_col_partitions > 1:
+            raise NotImplementedError("run_host is provided for the CSR form only")
         src = self._spec.inputs[0]
         for a, shape, what in ((x_host, src.shape, "x_host"), (y_host, self._spec.shape, "y_host")):
             if not (isinstance(a, torch.Tensor) and a.device.type == "cpu" and a.is_contiguous()
@@ -230,6 +279,8 @@ class SpMMbase(object):
     def set_poll_limit(self, polls):
         """Test hook: how often a wait inside the giant-row kernel polls before it gives up
         (negative: the default)."""
+        if self._num_col_partitions > 1:
+            raise NotImplementedError("the poll limit is a hook of the CSR form's plan")
         _lib.check(_lib.load().fg_spmm_plan_set_poll_limit(self._plan, int(polls)))
 
     def device_status(self):
@@ -239,16 +290,22 @@ class SpMMbase(object):
         if self._plan is None:
             return 0
         status = ctypes.c_int32(0)
-        _lib.check(_lib.load().fg_spmm_plan_status(self._plan, ctypes.byref(status)))
+        lib = _lib.load()
+        _lib.check((lib.fg_spmm_dds_plan_status if self._num_col_partitions > 1
+                    else lib.fg_spmm_plan_status)(self._plan, ctypes.byref(status)))
         return int(status.value)
 
     def num_launches(self):
         """Kernels launched per ``run`` call."""
-        return int(_lib.load().fg_spmm_plan_num_launches(self._plan)) if self._plan else 0
+        if not self._plan:
+            return 0
+        lib = _lib.load()
+        return int((lib.fg_spmm_dds_plan_num_launches if self._num_col_partitions > 1
+                    else lib.fg_spmm_plan_num_launches)(self._plan))
 
     def _release_plan(self):
         if getattr(self, "_plan", None):
-            _lib.load().fg_spmm_plan_destroy(self._plan)
+            self._destroy(self._plan)
             self._plan = None
 
     def __del__(self):
@@ -269,13 +326,16 @@ class SpMMbase(object):
 class VanillaSpMMcuda(SpMMbase):
     """CSR SpMM on the GPU (counterpart of VanillaSpMMcuda, spmm.py:212-220).
 
-    ``device_id`` (default 0, the reference's ``tvm.gpu(0)``) selects the GPU; it is the
-    one addition to the reference's constructor and exists for one-process-per-GPU runs.
+    ``device_id`` (default 0, the reference's ``tvm.gpu(0)``) selects the GPU; it exists
+    for one-process-per-GPU runs.  ``num_col_partitions`` > 1 (the reference offers it on
+    VanillaSpMMx86 only, spmm.py:197-209) selects the 1-D source-vertex partitioning: the
+    adjacency is converted to the DDS form and the column blocks are summed one after the
+    other, in the order of vanilla_spmm_dds_x86 (op/vanilla_spmm.py:149-220).
     """
 
-    def __init__(self, adj_scipy, device_id=0):
+    def __init__(self, adj_scipy, device_id=0, num_col_partitions=1):
         self._device_id = int(device_id)
-        super(VanillaSpMMcuda, self).__init__(adj_scipy, num_col_partitions=1)
+        super(VanillaSpMMcuda, self).__init__(adj_scipy, num_col_partitions)
 
     def _register(self):
         if not torch.cuda.is_available():
@@ -283,8 +343,12 @@ class VanillaSpMMcuda(SpMMbase):
         _lib.load()
         self._target = "cuda"
         self._ctx = gpu(self._device_id)
-        self._compute_func = vanilla_spmm_csr_cuda
-        self._schedule_func = schedule_vanilla_spmm_csr_cuda
+        if self._num_col_partitions > 1:
+            self._compute_func = vanilla_spmm_dds_cuda
+            self._schedule_func = schedule_vanilla_spmm_dds_cuda
+        else:
+            self._compute_func = vanilla_spmm_csr_cuda
+            self._schedule_func = schedule_vanilla_spmm_csr_cuda
 
 
 class VanillaSpMMx86(SpMMbase):

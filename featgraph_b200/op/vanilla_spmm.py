@@ -66,6 +66,38 @@ def schedule_vanilla_spmm_csr_x86(Out):
     raise no_x86("schedule_vanilla_spmm_csr_x86")
 
 
+def vanilla_spmm_dds_cuda(SrcFeat, Adj_s1_pos, Adj_s1_idx, Adj_vals, d1_size, d2_size):
+    """SpMM over the dense-dense-sparse form: the arguments of vanilla_spmm_dds_x86
+    (python/featgraph/op/vanilla_spmm.py:149-220) without its feature partitioning, which
+    only re-lays the arrays out.  The reference has this op for x86 only.
+
+    Out[row, f] = ((0 + S_0) + S_1) + ... with S_p[row, f] the sum, in stored order, of
+    Adj_vals[e] * SrcFeat[Adj_s1_idx[e] + p * ceil(num_src_vertices / d1_size), f] over the
+    entries Adj_s1_pos[p * d2_size + row] <= e < Adj_s1_pos[p * d2_size + row + 1].
+
+    SrcFeat : placeholder, (num_src_vertices, feat_len)
+    Adj_s1_pos : placeholder, (d1_size * d2_size,)
+    Adj_s1_idx, Adj_vals : placeholders, (nnz,)
+    d1_size : number of source-vertex partitions; d2_size : num_dst_vertices + 1
+    """
+    assert Adj_s1_pos.shape[0] == d1_size * d2_size
+    assert Adj_s1_idx.shape[0] == Adj_vals.shape[0]
+    if len(SrcFeat.shape) != 2:
+        raise ValueError("SrcFeat must be 2-D (num_src_vertices, feat_len), got %r"
+                         % (SrcFeat.shape,))
+    _, feat_len = SrcFeat.shape
+    return ComputeSpec("spmm_dds", (d2_size - 1, feat_len), SrcFeat.dtype,
+                       (SrcFeat, Adj_s1_pos, Adj_s1_idx, Adj_vals),
+                       {"msg_op": "mul", "reduce_op": "sum", "feat_len": feat_len,
+                        "num_col_partitions": int(d1_size)})
+
+
+def schedule_vanilla_spmm_dds_cuda(Out):
+    """Counterpart of schedule_vanilla_spmm_dds_x86 (vanilla_spmm.py:223-246) for the cuda
+    target; like it, it takes no knobs."""
+    return ScheduleSpec(Out, "cuda", {})
+
+
 def vanilla_spmm_dds_x86(SrcFeat, Adj_s1_pos, Adj_s1_idx, Adj_vals, d1_size, d2_size,
                          num_feat_partitions=1):
     """x86 DDS op of the reference (vanilla_spmm.py:149-220); not provided by this backend."""

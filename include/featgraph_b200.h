@@ -207,6 +207,42 @@ int fg_spmm_csr_f32_noalloc(const int32_t* indptr_dev, const int32_t* indices_de
 /* Largest n_rows fg_spmm_csr_f32_noalloc accepts. */
 int fg_spmm_noalloc_max_rows(void);
 
+/* ------------------------------------------- SpMM over column blocks (DDS) -- */
+
+/* The reference's 1-D source-vertex partitioning: vanilla_spmm_dds_x86 and its
+ * schedule (python/featgraph/op/vanilla_spmm.py:149-246), reached there through
+ * VanillaSpMMx86(adj, num_col_partitions > 1) (python/featgraph/module/spmm.py:41-56,
+ * 95-103).  The adjacency comes in the dense-dense-sparse form that
+ * util_convert_csr_to_dds makes (python/featgraph/util/adj_partitioning.py:7-57):
+ * the columns cut into P = num_col_partitions blocks of width ceil(n_cols / P),
+ * s1_pos holding P row-pointer arrays of n_rows + 1 entries each (positions into
+ * the arrays below, block after block), s1_idx block-local column indices.
+ *   S_p[row, f] = sum of vals[e] * X[s1_idx[e] + p * width, f] over the entries of
+ *                 block p's row, e ascending, accumulator starting at 0;
+ *   Y[row, f]   = ((0 + S_0) + S_1) + ... + S_(P-1), as the reference sums its
+ *                 Intermediate tensor over the block axis.
+ * Bit-identical to that order; NOT to fg_spmm_csr_f32's for P > 1 (different
+ * association; both agree with an exact sum to rounding).  The reference has this
+ * path for x86 only.
+ *
+ * The plan holds one CSR plan per block (s1_pos on the host); the call runs the
+ * blocks one after the other on the stream with the CSR kernels, each adding to
+ * Y, so that block p's gathers stay within its width * feat_len * 4 bytes of X. */
+typedef struct fg_spmm_dds_plan fg_spmm_dds_plan;
+int fg_spmm_dds_plan_create(const int32_t* s1_pos_host, int64_t n_rows, int64_t n_cols,
+                            int32_t feat_len, int32_t num_col_partitions, int32_t device,
+                            fg_spmm_dds_plan** out_plan);
+int fg_spmm_dds_plan_destroy(fg_spmm_dds_plan* plan);
+/* Kernels one fg_spmm_dds_f32 call launches. */
+int fg_spmm_dds_plan_num_launches(const fg_spmm_dds_plan* plan);
+/* fg_spmm_plan_status over every block's plan. */
+int fg_spmm_dds_plan_status(const fg_spmm_dds_plan* plan, int32_t* device_status);
+/* Y = A @ X from the DDS arrays on the device; asynchronous on `stream`.
+ * Launch options set by fg_next_launch_options are dropped, not applied. */
+int fg_spmm_dds_f32(const fg_spmm_dds_plan* plan, const int32_t* s1_pos_dev,
+                    const int32_t* s1_idx_dev, const float* vals_dev, const float* x_dev,
+                    float* y_dev, void* stream);
+
 /* ----------------------------------------------------------------- SDDMM -- */
 
 /* out[e, h] = sum over d < D of src[col[e], h*D + d] * dst[row[e], h*D + d],

@@ -274,3 +274,40 @@ int fg_oracle_gsddmm_coo_f32(int64_t nnz, int32_t feat_len, int32_t num_heads,
   }
   return 0;
 }
+
+/*
+ * SpMM over the dense-dense-sparse (DDS) form, the reference's 1-D source-vertex
+ * partitioning: python/featgraph/op/vanilla_spmm.py:149-220 with the schedule of
+ * :223-246.  The columns are cut into P blocks of width ceil(n_cols / P); block p holds
+ * its own CSR (row pointers s1_pos[p * (n_rows + 1) ...], block-local column indices).
+ *   Intermediate[p, row, f] = sum_e vals[e] * X[s1_idx[e] + p * width, f]   (:201-213)
+ *       e ascending within the block's row, accumulator starting at 0;
+ *   Out[row, f] = sum_p Intermediate[p, row, f]                             (:215-218)
+ *       p ascending, accumulator starting at 0 (so the first step is 0 + Intermediate[0]).
+ * The feature partitioning of the op (fo / fi) only re-lays the arrays out and is left
+ * out.  The per-block partial sums make this a DIFFERENT summation order from the CSR
+ * op's: the two agree to rounding (the reference's tests compare both with scipy at
+ * 1e-4), not bit for bit.  Rows are the parallel axis (:240-243).
+ */
+int fg_oracle_spmm_dds_f32(int64_t n_rows, int64_t n_cols, int32_t feat_len,
+                           int32_t num_col_partitions, const int32_t* s1_pos,
+                           const int32_t* s1_idx, const float* vals, const float* x, float* y) {
+  if (feat_len < 1 || num_col_partitions < 1) return 1;
+  const int64_t P = num_col_partitions;
+  const int64_t width = (n_cols + P - 1) / P;
+#pragma omp parallel for schedule(dynamic, 64)
+  for (int64_t row = 0; row < n_rows; ++row) {
+    float* out = y + row * feat_len;
+    for (int64_t f = 0; f < feat_len; ++f) out[f] = 0.0f;
+    for (int64_t p = 0; p < P; ++p) {
+      const int64_t beg = s1_pos[p * (n_rows + 1) + row], end = s1_pos[p * (n_rows + 1) + row + 1];
+      for (int64_t f = 0; f < feat_len; ++f) {
+        float acc = 0.0f;
+        for (int64_t e = beg; e < end; ++e)
+          acc = acc + vals[e] * x[((int64_t)s1_idx[e] + p * width) * feat_len + f];
+        out[f] = out[f] + acc;
+      }
+    }
+  }
+  return 0;
+}

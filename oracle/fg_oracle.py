@@ -181,3 +181,21 @@ def gsddmm_coo_f32(row, col, src, dst, num_heads=1, msg_op="mul", reduce_op="sum
     if rc != 0:
         raise ValueError("fg_oracle_gsddmm_coo_f32: bad argument")
     return res.reshape(nnz) if num_heads == 1 else res
+
+
+def spmm_dds_f32(s1_pos, s1_idx, vals, x, n_rows, num_col_partitions):
+    """Y = A @ X over the DDS form (vanilla_spmm.py:149-246): per column block a partial sum
+    in stored order, then the blocks' partial sums added in ascending block order."""
+    lib = _load()
+    lib.fg_oracle_spmm_dds_f32.argtypes = [
+        ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, _i32p, _i32p, _f32p,
+        _f32p, _f32p]
+    s1_pos, s1_idx = _c(s1_pos, np.int32), _c(s1_idx, np.int32)
+    vals, x = _c(vals, np.float32), _c(x, np.float32)
+    y = np.empty((n_rows, x.shape[1]), np.float32)
+    rc = lib.fg_oracle_spmm_dds_f32(n_rows, x.shape[0], x.shape[1], int(num_col_partitions),
+                                    _p(s1_pos, _i32p), _p(s1_idx, _i32p), _p(vals, _f32p),
+                                    _p(x, _f32p), _p(y, _f32p))
+    if rc != 0:
+        raise ValueError("fg_oracle_spmm_dds_f32: bad argument")
+    return y

@@ -81,3 +81,22 @@ def gsddmm_coo(row, col, src, dst, num_heads, msg_op, reduce_op):
                                                    np.float32(dst[row[e], k])))
             out[e, h] = acc
     return out.reshape(nnz) if num_heads == 1 else out
+
+
+def spmm_dds(s1_pos, s1_idx, vals, x, n_rows, num_col_partitions):
+    """vanilla_spmm.py:201-218: a partial sum per (column block, row), then the blocks'
+    partial sums added in ascending block order, both from an accumulator of 0."""
+    n_cols, f = x.shape
+    width = -(-n_cols // num_col_partitions)
+    y = np.zeros((n_rows, f), np.float32)
+    for r in range(n_rows):
+        for k in range(f):
+            total = np.float32(0.0)
+            for p in range(num_col_partitions):
+                acc = np.float32(0.0)
+                for e in range(s1_pos[p * (n_rows + 1) + r], s1_pos[p * (n_rows + 1) + r + 1]):
+                    prod = np.float32(np.float32(vals[e]) * np.float32(x[s1_idx[e] + p * width, k]))
+                    acc = np.float32(acc + prod)
+                total = np.float32(total + acc)
+            y[r, k] = total
+    return y

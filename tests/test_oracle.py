@@ -124,3 +124,21 @@ def test_generalised_oracle_with_mul_sum_is_the_reference_kernel(oracle):
     a = oracle.sddmm_coo_f32(coo.row, coo.col, x, dst, num_heads=4)
     b = oracle.gsddmm_coo_f32(coo.row, coo.col, x, dst, 4, "mul", "sum")
     assert np.array_equal(a.view(np.int32), b.view(np.int32))
+
+
+@pytest.mark.parametrize("parts", [1, 2, 4, 7])
+def test_dds_oracle(oracle, parts):
+    # the reference's x86 test runs the DDS op with 4 column partitions and compares with
+    # scipy at 1e-4 (tests/test_module_spmm.py:12-34); the C restatement is also checked bit
+    # for bit against the scalar Python spelling, and with one partition against the CSR op
+    from featgraph_b200.util import util_convert_csr_to_dds
+    adj = random_csr(127, 255, 0.1, seed=30 + parts, empty_rows=(0, 126))
+    x = features((255, 24), seed=31)
+    pos, idx, vals = util_convert_csr_to_dds(adj, parts)
+    y = oracle.spmm_dds_f32(pos, idx, vals, x, 127, parts)
+    np.testing.assert_allclose(adj.dot(x), y, rtol=1e-4, atol=1e-4)
+    want = py_restatement.spmm_dds(pos, idx, vals, x, 127, parts)
+    assert np.array_equal(want.view(np.int32), y.view(np.int32))
+    if parts == 1:
+        csr = oracle.spmm_csr_f32(adj.indptr, adj.indices, adj.data, x)
+        assert np.array_equal(bits(csr + np.float32(0.0)), bits(y))     # 0 + sum: -0 becomes +0

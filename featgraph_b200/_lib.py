@@ -34,10 +34,10 @@ EXPORTED_SYMBOLS = (
     "fg_spmm_csr_f32_mcast", "fg_sddmm_coo_f32_mcast", "fg_peer_barrier", "fg_gather_probe",
     "fg_spmm_csr_f32_general", "fg_sddmm_coo_f32_general", "fg_next_launch_options",
     "fg_spmm_dds_plan_create", "fg_spmm_dds_plan_destroy", "fg_spmm_dds_plan_num_launches",
-    "fg_spmm_dds_plan_status", "fg_spmm_dds_f32",
+    "fg_spmm_dds_plan_status", "fg_spmm_dds_f32", "fg_sddmm_status",
 )
 
-LAUNCH_PROGRAMMATIC, SPMM_GIANT_ROWS_ONLY, SPMM_SKIP_GIANT_ROWS = 1, 2, 4     # enum fg_launch_flags
+LAUNCH_PROGRAMMATIC, SPMM_GIANT_ROWS_ONLY, SPMM_SKIP_GIANT_ROWS, SDDMM_TMA_STAGING = 1, 2, 4, 8  # fg_launch_flags
 MSG_OPS = ("mul", "add", "sub", "div", "copy_lhs", "copy_rhs")    # enum fg_msg_op
 REDUCE_OPS = ("sum", "max", "min")                                # enum fg_reduce_op
 
@@ -67,6 +67,7 @@ def load():
     lib.fg_spmm_dds_plan_num_launches.argtypes = [c_void]
     lib.fg_spmm_dds_plan_status.argtypes = [c_void, c_i32p]
     lib.fg_spmm_dds_f32.argtypes = [c_void] * 7
+    lib.fg_sddmm_status.argtypes = [i32, c_i32p]
     lib.fg_spmm_csr_f32.argtypes = [c_void] * 7
     lib.fg_spmm_csr_f32_host.argtypes = [c_void] * 9
     lib.fg_spmm_csr_f32_multi.argtypes = [c_void] * 5 + [ctypes.POINTER(c_void), i32, c_void]

@@ -31,7 +31,8 @@ LaunchOptions take_launch_options() {
 }  // namespace fg
 
 extern "C" int fg_next_launch_options(int32_t flags, int32_t max_ctas) {
-  const int32_t known = FG_LAUNCH_PROGRAMMATIC | FG_SPMM_GIANT_ROWS_ONLY | FG_SPMM_SKIP_GIANT_ROWS;
+  const int32_t known = FG_LAUNCH_PROGRAMMATIC | FG_SPMM_GIANT_ROWS_ONLY |
+                        FG_SPMM_SKIP_GIANT_ROWS | FG_SDDMM_TMA_STAGING;
   if ((flags & ~known) != 0 || max_ctas < 0 ||
       ((flags & FG_SPMM_GIANT_ROWS_ONLY) && (flags & FG_SPMM_SKIP_GIANT_ROWS)))
     return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad launch options: flags=%d max_ctas=%d", (int)flags,

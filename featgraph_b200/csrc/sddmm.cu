@@ -17,6 +17,8 @@
 // run and read it back as a broadcast.
 //
 // sddmm_generic_kernel: any shape / alignment, one thread per (edge, head).
+#include <cuda.h>  // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only; no libcuda link)
+
 #include <algorithm>
 
 #include "common.cuh"
@@ -123,7 +125,10 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
       // .cg (no L1 allocation) although ncu shows that the bypass path brings 24 sectors per
       // warp-wide copy across the crossbar where the four 128-byte segments hold 16 (.ca
       // brings exactly 16): with .ca the kernel is SLOWER (3.55 against 2.81 ms at feat 64) --
-      // the L1's allocation work costs more than the extra sectors
+      // the L1's allocation work costs more than the extra sectors.  Loading the segments
+      // into registers and storing them with STS.128 (4 shared-memory wavefronts per warp-wide
+      // store where a cp.async deposit takes 9.5) is slower still: 4.3 to 6.1 ms with 30 to 24
+      // warps per SM -- the copy has to be asynchronous
       cp_async16_cg(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
     }
     if (staged) {
@@ -213,6 +218,266 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
   // covers both for whatever follows in the stream.
   if (blockIdx.x == gridDim.x - 1 && warp == 0) wait_for_prior_grids();
 }
+
+// ---- the same tiles staged by the tensor memory accelerator -------------------------
+//
+// sddmm_tma_kernel: sddmm_tile_kernel's arithmetic with the gathers handed to TMA.  A stage's
+// 32 src segments arrive as eight `cp.async.bulk.tensor.2d ... tile::gather4` copies (four
+// arbitrary rows of the feature matrix x 32 floats each, issued by eight lanes), its dst
+// segments as one or two more; the copies signal the stage's mbarrier with their byte
+// count.  The tensor maps use the 128-byte swizzle, so the 16-byte piece q of the row at
+// 128-byte slot r lies at piece q ^ (r & 7): lane l then reads ITS row with LDS.128 free of
+// bank conflicts without the padded pitch, and the TMA unit writes whole lines where the
+// sectors of a cp.async trickle into shared memory one by one.  Copies are asynchronous to
+// the warp, so a ring of kTmStages stages per warp is really in flight.
+//
+// Every wait on an mbarrier is bounded: after `max_wait` clock cycles the warp records 1 in
+// *status, stops issuing, waits (bounded again) for the copies it still has in flight and
+// returns; the results of its remaining edges are then not written.
+// Measured on B200 (114.6 M edges, feat_len 64; warps per CTA x stages per warp, warps per
+// SM): 6 x 1, 36: 3.57 ms; 4 x 2, 20: 3.88; 6 x 2, 18: 4.00; 4 x 3, 12: 4.70; 4 x 4, 8: 7.60
+// (sddmm_tile_kernel: 2.82).  More warps beat deeper rings here too, and every shape sits
+// on the TMA unit's rate of about one four-row gather per 16 cycles and SM.
+constexpr int kTmWarps = 6;
+constexpr int kTmStages = 1;
+constexpr int kTmMinCtas = 6;   // 36 warps per SM: at most 56 registers per thread
+constexpr int kTmSrcBytes = 32 * 128;                 // 32 edges x 32 floats
+constexpr int kTmDstBytes = kSdDstSlots * 128;        // up to 8 distinct dst rows
+constexpr int kTmStageBytes = kTmSrcBytes + kTmDstBytes;
+constexpr int kTmMetaInts = 32 + kSdDstSlots;         // per-lane words, slot rows
+constexpr int kTmSmemBytes = 1024 + kTmWarps * kTmStages * (kTmStageBytes + 8 + 4 * kTmMetaInts);
+constexpr long long kTmMaxWaitCycles = 4000000000LL;  // about two seconds
+// how long one try_wait may keep the thread suspended (it wakes when the phase completes);
+// without the hint the waiting warps poll, and their polls take issue slots
+constexpr unsigned kTmSuspendNs = 2000;
+static_assert(kTmStageBytes % 1024 == 0, "stages keep the swizzle's 1024-byte period");
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(kTmSuspendNs)
+      : "memory");
+  return ok != 0;
+}
+// Rows r0..r3 of the 2-D tensor behind `map`, 32 floats from column x (x * 4 is a multiple
+// of 16 bytes: every chunk starts at a multiple of 32 floats), to 512 bytes at smem_dst.
+__device__ __forceinline__ void tma_gather4(uint32_t smem_dst, const CUtensorMap* map, int x,
+                                            int r0, int r1, int r2, int r3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(r0), "r"(r1), "r"(r2),
+        "r"(r3), "r"(bar)
+      : "memory");
+}
+
+template <int HEAD_DIM, int MSG, int RED>
+__global__ void __launch_bounds__(kTmWarps * 32, kTmMinCtas)
+sddmm_tma_kernel(const int* __restrict__ row, const int* __restrict__ col,
+                 const __grid_constant__ CUtensorMap src_map,
+                 const __grid_constant__ CUtensorMap dst_map, const float* __restrict__ dst,
+                 const __grid_constant__ OutPtrs out, long long nnz, int F, int H,
+                 int tiles_per_warp, int vec_heads, int* __restrict__ status,
+                 long long max_wait) {
+  constexpr unsigned kFull = 0xffffffffu;
+  extern __shared__ unsigned char tm_smem[];
+  launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+
+  const long long n_tiles = (nnz + 31) / 32;
+  const long long tile0 = ((long long)blockIdx.x * kTmWarps + warp) * tiles_per_warp;
+  if (tile0 >= n_tiles) return;  // (warp 0 of every CTA has tiles)
+  const int my_tiles = (int)min((long long)tiles_per_warp, n_tiles - tile0);
+  const int n_chunks = F / kSdChunk;
+  const int total = my_tiles * n_chunks;
+  const int chunks_per_head = HEAD_DIM == 0 ? (F / H) / kSdChunk : 1;
+
+  // this warp's stages (1024-byte aligned), barriers and per-stage words
+  const uint32_t raw = smem_u32(tm_smem);
+  const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
+  unsigned char* stages_gen = tm_smem + pad + (size_t)warp * kTmStages * kTmStageBytes;
+  const uint32_t stages = raw + pad + warp * kTmStages * kTmStageBytes;
+  const uint32_t bars = raw + pad + kTmWarps * kTmStages * kTmStageBytes + warp * kTmStages * 8;
+  int* meta = reinterpret_cast<int*>(tm_smem + pad + kTmWarps * kTmStages * (kTmStageBytes + 8)) +
+              warp * kTmStages * kTmMetaInts;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kTmStages; ++s) mbar_init(bars + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+
+  int r_iss = 0, c_iss = 0, word_iss = 0, n_slots = 1;
+  bool head_iss = false;
+  int r_ahead = 0, c_ahead = 0;
+  auto fetch_indices = [&](int t) {
+    const long long e = (tile0 + t) * 32 + lane;
+    r_ahead = 0;
+    c_ahead = 0;
+    if (t < my_tiles && e < nnz) {
+      r_ahead = ld_stream(row + e);
+      c_ahead = ld_stream(col + e);
+    }
+  };
+  auto begin_tile = [&](int t) {  // as in sddmm_tile_kernel
+    r_iss = r_ahead;
+    c_iss = c_ahead;
+    fetch_indices(t + 1);
+    const int r_left = __shfl_up_sync(kFull, r_iss, 1);
+    head_iss = lane == 0 || r_iss != r_left;
+    const unsigned run_heads = __ballot_sync(kFull, head_iss);
+    n_slots = __popc(run_heads);
+    const int slot = __popc(run_heads & (0xffffffffu >> (31 - lane))) - 1;
+    word_iss = n_slots <= kSdDstSlots ? slot : -1 - r_iss;
+  };
+  int t_iss = 0, ch_iss = 0;
+  auto issue = [&](int buf) {
+    if (ch_iss == 0) begin_tile(t_iss);
+    int* words = meta + buf * kTmMetaInts;
+    int* slot_rows = words + 32;
+    const bool staged = n_slots <= kSdDstSlots;
+    words[lane] = word_iss;
+    if (staged && head_iss) slot_rows[word_iss] = r_iss;
+    const int n_dst = staged ? (n_slots > 4 ? 2 : 1) : 0;
+    const uint32_t bar = bars + 8 * buf;
+    if (lane == 0) mbar_arrive_expect_tx(bar, kTmSrcBytes + 512 * n_dst);
+    // the lanes' reads of this buffer (generic proxy) come before the copies into it
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    const int x = ch_iss * kSdChunk;
+    const uint32_t sdst = stages + buf * kTmStageBytes;
+    const int g = (lane & 7) * 4;
+    const int c0 = __shfl_sync(kFull, c_iss, g), c1 = __shfl_sync(kFull, c_iss, g + 1);
+    const int c2 = __shfl_sync(kFull, c_iss, g + 2), c3 = __shfl_sync(kFull, c_iss, g + 3);
+    if (lane < 8) {
+      tma_gather4(sdst + 512 * lane, &src_map, x, c0, c1, c2, c3, bar);
+    } else if (lane < 8 + n_dst) {
+      const int s0 = 4 * (lane - 8), last = n_slots - 1;
+      tma_gather4(sdst + kTmSrcBytes + 512 * (lane - 8), &dst_map, x, slot_rows[min(s0, last)],
+                  slot_rows[min(s0 + 1, last)], slot_rows[min(s0 + 2, last)],
+                  slot_rows[min(s0 + 3, last)], bar);
+    }
+    if (++ch_iss == n_chunks) {
+      ch_iss = 0;
+      ++t_iss;
+    }
+  };
+  auto wait_stage = [&](int buf, unsigned parity) -> bool {
+    bool ok = mbar_try_wait(bars + 8 * buf, parity);
+    if (!ok) {
+      const long long t0 = clock64();
+      do {
+        ok = mbar_try_wait(bars + 8 * buf, parity);
+      } while (!ok && clock64() - t0 < max_wait);
+    }
+    return __all_sync(kFull, ok);
+  };
+
+  fetch_indices(0);
+  int issued = 0;
+#pragma unroll
+  for (int p = 0; p < kTmStages - 1; ++p)
+    if (p < total) {
+      issue(p);
+      ++issued;
+    }
+  float acc = red_identity<RED>();
+  int head = 0, chunk = 0, buf = 0, buf_issue = kTmStages - 1;
+  unsigned parity = 0;
+  long long e = tile0 * 32 + lane;
+  float4 pend = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto finish_head = [&]() {  // as in sddmm_tile_kernel
+    if (vec_heads) {
+      switch (head & 3) {
+        case 0: pend.x = acc; break;
+        case 1: pend.y = acc; break;
+        case 2: pend.z = acc; break;
+        default:
+          pend.w = acc;
+          if (e < nnz) out_store(out, (size_t)e * H + head - 3, pend);
+      }
+    } else if (e < nnz) {
+      out_store(out, (size_t)e * H + head, acc);
+    }
+    ++head;
+    acc = red_identity<RED>();
+  };
+  int it = 0;
+  bool gave_up = false;
+  for (; it < total; ++it) {
+    if (issued < total) {
+      issue(buf_issue);
+      ++issued;
+    }
+    if (!wait_stage(buf, parity)) {
+      gave_up = true;
+      break;
+    }
+    const unsigned char* stage = stages_gen + buf * kTmStageBytes;
+    const int word = meta[buf * kTmMetaInts + lane];
+    const unsigned char* srow = stage + lane * 128;
+    const int sx = (lane & 7) << 4;
+    const unsigned char* drow = stage + kTmSrcBytes + (word >= 0 ? word : 0) * 128;
+    const int dx = word >= 0 ? (word & 7) << 4 : 0;
+    const float4* dglob = reinterpret_cast<const float4*>(
+        dst + (size_t)(word >= 0 ? 0 : -1 - word) * F + (size_t)chunk * kSdChunk);
+#pragma unroll
+    for (int q = 0; q < kSdChunk / 4; ++q) {
+      const float4 a = *reinterpret_cast<const float4*>(srow + ((q << 4) ^ sx));
+      const float4 b = word >= 0 ? *reinterpret_cast<const float4*>(drow + ((q << 4) ^ dx))
+                                 : dglob[q];
+      acc = combine<MSG, RED>(acc, a.x, b.x);
+      acc = combine<MSG, RED>(acc, a.y, b.y);
+      acc = combine<MSG, RED>(acc, a.z, b.z);
+      acc = combine<MSG, RED>(acc, a.w, b.w);
+      if (HEAD_DIM > 0 && ((q + 1) * 4) % (HEAD_DIM > 0 ? HEAD_DIM : 4) == 0) finish_head();
+    }
+    ++chunk;
+    if (HEAD_DIM == 0 && chunk % chunks_per_head == 0) finish_head();
+    if (chunk == n_chunks) {
+      chunk = 0;
+      head = 0;
+      acc = red_identity<RED>();
+      e += 32;
+    }
+    if (++buf == kTmStages) {
+      buf = 0;
+      parity ^= 1u;
+    }
+    buf_issue = buf_issue == kTmStages - 1 ? 0 : buf_issue + 1;
+    __syncwarp();  // every lane is done with this buffer before it is refilled
+  }
+  if (gave_up) {
+    if (lane == 0) atomicCAS(status, 0, 1);
+    // the copies still in flight land in this CTA's shared memory: stay until they have
+    // (bounded), starting with the stage that was being waited for
+    for (int k = it; k < issued; ++k) {
+      wait_stage(buf, parity);
+      if (++buf == kTmStages) {
+        buf = 0;
+        parity ^= 1u;
+      }
+    }
+  }
+  if (blockIdx.x == gridDim.x - 1 && warp == 0) wait_for_prior_grids();
+}
+
+// Status word of the TMA kernel's bounded waits, one per GPU (fg_sddmm_status).
+static __device__ int g_sddmm_status;
 
 template <int MSG, int RED>
 __global__ void __launch_bounds__(256)
@@ -350,12 +615,56 @@ static cudaError_t launch_kernel(void (*kernel)(Params...), unsigned grid, unsig
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against
+// libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Tensor map of a row-major (rows x F) float matrix for tile::gather4 copies of 32-float
+// row segments: a box of one row x 32 floats, 128-byte swizzle.
+static bool make_segment_map(CUtensorMap* map, const float* base, int64_t rows, int32_t F) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || rows < 1) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)F, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)F * sizeof(float)};
+  const cuuint32_t box[2] = {(cuuint32_t)kSdChunk, 1};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box,
+            elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int* sddmm_status_word(int device) {
+  static thread_local int* words[64] = {nullptr};
+  if (device < 0 || device >= 64) return nullptr;
+  if (!words[device]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_sddmm_status) != cudaSuccess) return nullptr;
+    words[device] = static_cast<int*>(p);
+  }
+  return words[device];
+}
+
 template <int MSG, int RED>
 static cudaError_t sddmm_launch_kernels(int variant, long long grid, int tiles_per_warp,
                                         bool programmatic, const int32_t* row,
                                         const int32_t* col, const float* src, const float* dst,
-                                        const OutPtrs& out, int64_t nnz, int32_t feat_len,
-                                        int32_t num_heads, int32_t device, cudaStream_t st) {
+                                        const OutPtrs& out, int64_t nnz, int64_t n_rows,
+                                        int64_t n_cols, int32_t feat_len, int32_t num_heads,
+                                        int32_t device, cudaStream_t st, bool tma) {
   // heads leave four at a time where the lane's four results are one aligned 16-byte piece
   int vec_heads = num_heads % 4 == 0;
   for (int q = 0; q < out.n; ++q)
@@ -363,6 +672,40 @@ static cudaError_t sddmm_launch_kernels(int variant, long long grid, int tiles_p
   if (variant < 0)
     return launch_kernel(sddmm_generic_kernel<MSG, RED>, (unsigned)grid, 256, 0, st, programmatic,
                          row, col, src, dst, out, (long long)nnz * num_heads, feat_len, num_heads);
+  if (tma && !(MSG == FG_MSG_MUL && RED == FG_REDUCE_SUM)) return cudaErrorNotSupported;
+  if constexpr (MSG == FG_MSG_MUL && RED == FG_REDUCE_SUM) if (tma) {
+    CUtensorMap src_map, dst_map;
+    int* status = sddmm_status_word(device);
+    if (!status || !make_segment_map(&src_map, src, n_cols, feat_len) ||
+        !make_segment_map(&dst_map, dst, n_rows, feat_len))
+      return cudaErrorInvalidValue;
+#define FG_SD_LAUNCH_TMA(HPC)                                                                 \
+  do {                                                                                        \
+    static thread_local int configured_dev = -1;                                              \
+    if (configured_dev != device) {                                                           \
+      cudaError_t e__ = cudaFuncSetAttribute(sddmm_tma_kernel<HPC, MSG, RED>,                 \
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                             kTmSmemBytes);                                   \
+      if (e__ != cudaSuccess) return e__;                                                     \
+      configured_dev = device;                                                                \
+    }                                                                                         \
+    cudaError_t l__ = launch_kernel(sddmm_tma_kernel<HPC, MSG, RED>, (unsigned)grid,          \
+                                    kTmWarps * 32, kTmSmemBytes, st, programmatic, row, col,  \
+                                    src_map, dst_map, dst, out, (long long)nnz, feat_len,     \
+                                    num_heads, tiles_per_warp, vec_heads, status,             \
+                                    kTmMaxWaitCycles);                                        \
+    if (l__ != cudaSuccess) return l__;                                                       \
+  } while (0)
+    switch (variant) {
+      case 0: FG_SD_LAUNCH_TMA(0); break;
+      case 4: FG_SD_LAUNCH_TMA(4); break;
+      case 8: FG_SD_LAUNCH_TMA(8); break;
+      case 16: FG_SD_LAUNCH_TMA(16); break;
+      default: FG_SD_LAUNCH_TMA(32); break;
+    }
+#undef FG_SD_LAUNCH_TMA
+    return cudaGetLastError();
+  }
 #define FG_SD_LAUNCH(HPC)                                                                     \
   do {                                                                                        \
     static thread_local int configured_dev = -1;                                              \
@@ -431,6 +774,11 @@ static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src
   const bool aligned = (reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(dst) % 16 == 0);
   const int variant = aligned ? sddmm_variant(feat_len, num_heads) : -1;
+  const bool tma = (opt.flags & FG_SDDMM_TMA_STAGING) != 0;
+  if (tma && (variant < 0 || msg_op != FG_MSG_MUL || reduce_op != FG_REDUCE_SUM))
+    return fail(FG_ERR_UNSUPPORTED, "FG_SDDMM_TMA_STAGING needs the multiply / sum operator pair, "
+                "feat_len a multiple of 32 and 16-byte aligned feature arrays");
+  const int warps = tma ? kTmWarps : kSdWarps;
   long long grid;
   long long tiles_per_warp = kSdTilesPerWarp;
   if (variant < 0) {
@@ -441,9 +789,9 @@ static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src
     // a bounded grid (max_ctas): every warp walks a longer stretch of the edge list
     if (opt.max_ctas > 0)
       tiles_per_warp = std::max<long long>(
-          tiles_per_warp, (tiles + (long long)kSdWarps * opt.max_ctas - 1) / ((long long)kSdWarps * opt.max_ctas));
+          tiles_per_warp, (tiles + (long long)warps * opt.max_ctas - 1) / ((long long)warps * opt.max_ctas));
     if (tiles_per_warp >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "edge count too large");
-    const long long per_cta = (long long)kSdWarps * tiles_per_warp;
+    const long long per_cta = (long long)warps * tiles_per_warp;
     grid = (tiles + per_cta - 1) / per_cta;
     if (grid >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "edge count too large");
   }
@@ -451,10 +799,34 @@ static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src
   cudaError_t err = cudaSuccess;
 #define FG_SD_OPS(M, R)                                                                          \
   err = sddmm_launch_kernels<M, R>(variant, grid, (int)tiles_per_warp, programmatic, row, col,  \
-                                   src, dst, out, nnz, feat_len, num_heads, device, st)
+                                   src, dst, out, nnz, n_rows, n_cols, feat_len, num_heads,     \
+                                   device, st, tma)
   FG_DISPATCH_OPS(msg_op, reduce_op, FG_SD_OPS);
 #undef FG_SD_OPS
   FG_CUDA_TRY(err);
+  return FG_OK;
+}
+
+extern "C" int fg_sddmm_status(int32_t device, int32_t* device_status) {
+  using namespace fg;
+  if (!device_status) return fail(FG_ERR_INVALID_ARGUMENT, "device_status is null");
+  *device_status = 0;
+  DeviceGuard guard(device);
+  if (guard.status != cudaSuccess)
+    return fail(FG_ERR_CUDA, "cannot select device %d: %s", device,
+                cudaGetErrorString(guard.status));
+  int* word = sddmm_status_word(device);
+  if (!word) return fail(FG_ERR_CUDA, "cannot find the status word");
+  FG_CUDA_TRY(cudaDeviceSynchronize());
+  int v = 0;
+  FG_CUDA_TRY(cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost));
+  *device_status = v;
+  if (v != 0) {
+    // reported once: the word is cleared so that later calls are judged on their own
+    FG_CUDA_TRY(cudaMemset(word, 0, sizeof(int)));
+    return fail(FG_ERR_CUDA, "sddmm_tma_kernel: a bounded wait for a TMA copy gave up; the "
+                "results of the edges behind it were not written");
+  }
   return FG_OK;
 }
 

@@ -721,6 +721,7 @@ struct fg_spmm_plan {
   int* status_dev = nullptr;  // set by a giant-kernel wait that gave up
   unsigned poll_limit = 0;    // polls a chain-kernel wait makes before it gives up
   int l2_bytes = 0, n_sms = 0;
+  bool slabs_together = false;  // one launch per class over all slabs (experiments only)
 };
 
 namespace fg {
@@ -850,17 +851,19 @@ static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, in
     // its throughput time and the longest row's chain in the giant kernel; a shard of
     // a multi-GPU run has less of the former, so more of its rows turn giant.  The
     // giant kernel gives an SM to 32 floats of one row, so it is kept for such rows.
-    const double t_throughput = (double)p->nnz * (feat_len / 32.0) * kCyclesPerNnzSlab * 148.0 /
-                                std::max(1, p->n_sms);
-    const double t_call = std::max(t_throughput, (double)max_deg * kGiantCyclesPerNnz);
-    // the light kernel serves its items one residency slab after the other, so a light row
-    // has to fit one such pass, not the whole call
-    const double t_pass = t_call * p->slab_w / feat_len;
     double light_div = kLightCyclesPerNnzOfPass, giant_share = kGiantShareOfCall;
 #ifdef FG_TUNING
     if (const char* e = getenv("FG_LIGHT_DIV")) light_div = atof(e);
     if (const char* e = getenv("FG_GIANT_FRAC")) giant_share = atof(e);
+    if (const char* e = getenv("FG_SLABS_TOGETHER")) p->slabs_together = atoi(e) != 0;
 #endif
+    // the floats of a row that one giant / heavy / light trio covers: the residency slab
+    const int width = p->slabs_together ? feat_len : p->slab_w;
+    const double t_throughput = (double)p->nnz * (width / 32.0) * kCyclesPerNnzSlab * 148.0 /
+                                std::max(1, p->n_sms);
+    const double t_call = std::max(t_throughput, (double)max_deg * kGiantCyclesPerNnz);
+    // a light row has to fit the pass over one residency slab
+    const double t_pass = t_call * p->slab_w / width;
     // Heavy class: the light kernel moves about twice the nonzeros per SM-cycle of the heavy
     // one (its gathers go straight to registers; the heavy and giant kernels pass every
     // gathered byte through shared memory) but walks a row at about one gather latency per 8
@@ -970,7 +973,8 @@ extern "C" int fg_spmm_plan_set_poll_limit(fg_spmm_plan* p, int64_t polls) {
 extern "C" int fg_spmm_plan_num_launches(const fg_spmm_plan* p) {
   if (!p || p->n_rows == 0) return 0;
   if (!p->vector_ok) return 1;
-  return (p->n_giant > 0 ? 1 : 0) + (p->n_heavy > 0 ? 1 : 0) + (p->n_light > 0 ? 1 : 0);
+  const int trios = p->slabs_together ? 1 : p->feat_len / p->slab_w;
+  return trios * ((p->n_giant > 0 ? 1 : 0) + (p->n_heavy > 0 ? 1 : 0) + (p->n_light > 0 ? 1 : 0));
 }
 
 extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t buf_len) {
@@ -978,22 +982,24 @@ extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t b
   if (!p || !buf || buf_len <= 0) return fail(FG_ERR_INVALID_ARGUMENT, "null plan or buffer");
   if (p->vector_ok) {
     const int G = p->slab_w / 4;
-    const int hv_slabs = p->feat_len / (32 * p->heavy_vec);
-    const long long light_items = (long long)p->n_light * (p->feat_len / p->slab_w);
+    // grids of ONE trio: the kernels run once per residency slab of the features
+    const int width = p->slabs_together ? p->feat_len : p->slab_w;
+    const int hv_slabs = width / (32 * p->heavy_vec);
+    const long long light_items = (long long)p->n_light * (width / p->slab_w);
     snprintf(buf, (size_t)buf_len,
              "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d max_deg=%lld | L2=%d B "
              "slab_w=%d | light: %d rows (deg<=%d) -> spmm_light_kernel<G=%d> grid=%lld x 256 thr | "
              "heavy: %d rows (deg<=%d), %lld nnz -> spmm_heavy_kernel<VEC=%d> grid=%lld x 32 thr, "
              "%d-stage cp.async ring | giant: %d rows, %lld nnz -> "
              "spmm_chain_kernel grid=%lld x %d thr (%d producer warps + 1 consumer, "
-             "%d-block ring of products, flag words); launch order giant, heavy, light, "
-             "programmatic dependent launches",
+             "%d-block ring of products, flag words); %d slab(s) one after the other, each: "
+             "giant, heavy, light, chained by programmatic dependent launches",
              (long long)p->n_rows, (long long)p->n_cols, (long long)p->nnz, p->feat_len,
              (long long)p->max_deg, p->l2_bytes, p->slab_w, p->n_light, p->heavy_threshold, G,
              (light_items + 256 / G - 1) / (256 / G), p->n_heavy, p->giant_threshold,
              (long long)p->heavy_nnz, p->heavy_vec, (long long)p->n_heavy * hv_slabs, kHvXSlots,
-             p->n_giant, (long long)p->giant_nnz, (long long)p->n_giant * (p->feat_len / 32),
-             32 * GiantShape::WARPS, GiantShape::PRODUCERS, GiantShape::RING);
+             p->n_giant, (long long)p->giant_nnz, (long long)p->n_giant * (width / 32),
+             32 * GiantShape::WARPS, GiantShape::PRODUCERS, GiantShape::RING, p->feat_len / width);
   } else {
     snprintf(buf, (size_t)buf_len,
              "spmm_csr_f32 rows=%lld cols=%lld nnz=%lld feat_len=%d | spmm_generic_kernel "
@@ -1043,9 +1049,9 @@ static cudaError_t launch_kernel(void (*kernel)(Params...), unsigned grid, unsig
 template <int G, int U, int MSG, int RED>
 static cudaError_t launch_light(const fg_spmm_plan* p, const int32_t* indptr,
                                 const int32_t* indices, const float* vals, const float* x,
-                                const OutPtrs& y, int first, int n_listed, cudaStream_t st,
-                                bool programmatic) {
-  const long long items = (long long)n_listed * (p->feat_len / (4 * G));
+                                const OutPtrs& y, int first, int n_listed, int width,
+                                cudaStream_t st, bool programmatic) {
+  const long long items = (long long)n_listed * (width / (4 * G));
   const long long grid = (items + 256 / G - 1) / (256 / G);
   return launch_kernel(spmm_light_kernel<G, U, MSG, RED>, (unsigned)grid, 256, 0, st, programmatic,
                        indptr, indices, vals, x, y, p->rows_dev + first, n_listed, items,
@@ -1055,13 +1061,13 @@ static cudaError_t launch_light(const fg_spmm_plan* p, const int32_t* indptr,
 template <class Shape, int MSG, int RED>
 static cudaError_t launch_chain(const fg_spmm_plan* p, const int32_t* indptr,
                                 const int32_t* indices, const float* vals, const float* x,
-                                const OutPtrs& y, int first, int n_listed, cudaStream_t st,
-                                bool programmatic) {
+                                const OutPtrs& y, int first, int n_listed, int width,
+                                cudaStream_t st, bool programmatic) {
   const cudaError_t e =
       ensure_smem<spmm_chain_kernel<Shape, MSG, RED>>(Shape::SMEM_BYTES, p->device);
   if (e != cudaSuccess) return e;
   // one CTA per (row, 32-float slab)
-  const unsigned grid = (unsigned)(n_listed * (p->feat_len / 32));
+  const unsigned grid = (unsigned)(n_listed * (width / 32));
   return launch_kernel(spmm_chain_kernel<Shape, MSG, RED>, grid, 32 * Shape::WARPS,
                        Shape::SMEM_BYTES, st, programmatic, indptr, indices, vals, x, y,
                        p->rows_dev + first, n_listed, p->slab_w / 32, p->feat_len, p->status_dev,
@@ -1071,12 +1077,13 @@ static cudaError_t launch_chain(const fg_spmm_plan* p, const int32_t* indptr,
 template <int VEC, int MSG, int RED>
 static cudaError_t launch_heavy(const fg_spmm_plan* p, const int32_t* indptr,
                                 const int32_t* indices, const float* vals, const float* x,
-                                const OutPtrs& y, cudaStream_t st, bool programmatic) {
+                                const OutPtrs& y, int width, cudaStream_t st,
+                                bool programmatic) {
   const cudaError_t e =
       ensure_smem<spmm_heavy_kernel<VEC, MSG, RED>>(heavy_smem_bytes<VEC>(), p->device);
   if (e != cudaSuccess) return e;
   const int slab = 32 * VEC;
-  const long long items = (long long)p->n_heavy * (p->feat_len / slab);  // < INT32_MAX (plan)
+  const long long items = (long long)p->n_heavy * (width / slab);  // < INT32_MAX (plan)
   return launch_kernel(spmm_heavy_kernel<VEC, MSG, RED>, (unsigned)items, 32,
                        heavy_smem_bytes<VEC>(), st, programmatic, indptr, indices, vals, x, y,
                        p->rows_dev + p->n_giant, p->n_heavy, p->slab_w / slab, p->feat_len);
@@ -1100,20 +1107,6 @@ static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const i
     return FG_OK;
   }
 
-  auto light = [&](cudaStream_t stream, bool programmatic) -> cudaError_t {
-    const int first = p->n_giant + p->n_heavy;
-    switch (p->slab_w) {
-      case 128: return launch_light<32, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, stream, programmatic);
-      case 64: return launch_light<16, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, stream, programmatic);
-      default: return launch_light<8, 8, MSG, RED>(p, indptr, indices, vals, x, y, first, p->n_light, stream, programmatic);
-    }
-  };
-  auto heavy = [&](cudaStream_t stream, bool programmatic) -> cudaError_t {
-    return p->heavy_vec == 2
-               ? launch_heavy<2, MSG, RED>(p, indptr, indices, vals, x, y, stream, programmatic)
-               : launch_heavy<1, MSG, RED>(p, indptr, indices, vals, x, y, stream, programmatic);
-  };
-
   // One stream, longest rows first: giant kernel, heavy kernel, light kernel, each
   // dispatched as soon as every CTA of the one before it is resident (programmatic
   // dependent launch) -- not when it has completed; the three write disjoint rows.  A
@@ -1122,20 +1115,46 @@ static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const i
   // giant rows, the call's critical path, start when the light kernel is nearly done.
   // (Measured with the three kernels on three streams and fork / join events instead:
   // 2.02 or 2.45 ms per call, depending on which launch reached the GPU first; this
-  // way 1.875 ms, every time.)  The last CTA of the heavy and of the light kernel waits
-  // for the grids before it, so whatever follows in the stream sees the whole SpMM
-  // complete.
-  if (giants && p->n_giant > 0) {
-    FG_CUDA_TRY((launch_chain<GiantShape, MSG, RED>(p, indptr, indices, vals, x, y, 0, p->n_giant,
-                                                    st, any)));
-    any = true;
+  // way 1.875 ms, every time.)  The last CTA of every kernel waits for the grids before
+  // it, so whatever follows in the stream sees the whole SpMM complete.
+  //
+  // One such trio per residency slab, slab after slab: the three kernels of a trio then
+  // gather from the SAME slab of X.  In one launch over all slabs each kernel walks the
+  // slabs at its own pace, two or three slabs are live at a time, and together they no
+  // longer fit L2.
+  const int width = p->slabs_together ? p->feat_len : p->slab_w;
+  int f_end = p->feat_len;
+#ifdef FG_TUNING
+  if (const char* e = getenv("FG_FIRST_TRIOS")) f_end = std::min(f_end, atoi(e) * width);
+#endif
+  for (int f0 = 0; f0 < f_end; f0 += width) {
+    const float* xs = x + f0;
+    OutPtrs ys = y;
+    for (int q = 0; q < ys.n; ++q) ys.p[q] += f0;
+    if (giants && p->n_giant > 0) {
+      FG_CUDA_TRY((launch_chain<GiantShape, MSG, RED>(p, indptr, indices, vals, xs, ys, 0,
+                                                      p->n_giant, width, st, any)));
+      any = true;
+    }
+    if (!rest) continue;
+    if (p->n_heavy > 0) {
+      FG_CUDA_TRY((p->heavy_vec == 2
+                       ? launch_heavy<2, MSG, RED>(p, indptr, indices, vals, xs, ys, width, st, any)
+                       : launch_heavy<1, MSG, RED>(p, indptr, indices, vals, xs, ys, width, st, any)));
+      any = true;
+    }
+    if (p->n_light > 0) {
+      const int first = p->n_giant + p->n_heavy;
+      cudaError_t e;
+      switch (p->slab_w) {
+        case 128: e = launch_light<32, 8, MSG, RED>(p, indptr, indices, vals, xs, ys, first, p->n_light, width, st, any); break;
+        case 64: e = launch_light<16, 8, MSG, RED>(p, indptr, indices, vals, xs, ys, first, p->n_light, width, st, any); break;
+        default: e = launch_light<8, 8, MSG, RED>(p, indptr, indices, vals, xs, ys, first, p->n_light, width, st, any); break;
+      }
+      FG_CUDA_TRY(e);
+      any = true;
+    }
   }
-  if (!rest) return FG_OK;
-  if (p->n_heavy > 0) {
-    FG_CUDA_TRY(heavy(st, any));
-    any = true;
-  }
-  if (p->n_light > 0) FG_CUDA_TRY(light(st, any));
   return FG_OK;
 }
 

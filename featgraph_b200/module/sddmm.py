@@ -223,6 +223,15 @@ class SDDMMbase(object):
             self._ctx.device_id, current_stream_handle(self._ctx)))
         return out_host
 
+    def device_status(self):
+        """Synchronise and return the status word of the kernel that stages its tiles with
+        TMA copies (``launch_flags=_lib.SDDMM_TMA_STAGING``): 0 when every bounded wait
+        completed; raises FeatGraphError otherwise (once: the word is then cleared)."""
+        import ctypes
+        status = ctypes.c_int32(0)
+        _lib.check(_lib.load().fg_sddmm_status(self._ctx.device_id, ctypes.byref(status)))
+        return int(status.value)
+
     def num_launches(self):
         if self._spec is None:
             return 0

@@ -295,6 +295,14 @@ class SpMMbase(object):
                     else lib.fg_spmm_plan_status)(self._plan, ctypes.byref(status)))
         return int(status.value)
 
+    def describe(self):
+        """One line on the built plan: row classes, kernels and grids (the CSR form)."""
+        if not self._plan or self._num_col_partitions > 1:
+            return ""
+        buf = ctypes.create_string_buffer(2048)
+        _lib.check(_lib.load().fg_spmm_plan_describe(self._plan, buf, len(buf)))
+        return buf.value.decode()
+
     def num_launches(self):
         """Kernels launched per ``run`` call."""
         if not self._plan:

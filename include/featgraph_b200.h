@@ -71,11 +71,19 @@ const char* fg_version(void);
  *   plan's giant rows / everything but them; the two calls together are one SpMM.
  * max_ctas > 0 (SDDMM): at most this many CTAs, each walking more edges, so that the whole
  *   grid is resident at once and the kernel behind it can be dispatched beside it.
+ * FG_SDDMM_TMA_STAGING (SDDMM, multiply / sum, feat_len a multiple of 32): the gathered
+ *   feature segments are brought into shared memory by the tensor memory accelerator
+ *   (cp.async.bulk.tensor tile::gather4 copies, 128-byte swizzle, mbarriers with bounded
+ *   waits; see fg_sddmm_status) instead of by the lanes' cp.async copies.  Same results
+ *   bit for bit.  Measured slower on B200 for 128-byte segments (3.57 against 2.82 ms at
+ *   feat_len 64 on 114.6 M edges: the TMA unit takes about 16 cycles per four-row gather),
+ *   so it is not the default.
  * The reference has no counterpart (one kernel, one stream). */
 enum fg_launch_flags {
   FG_LAUNCH_PROGRAMMATIC = 1,
   FG_SPMM_GIANT_ROWS_ONLY = 2,
-  FG_SPMM_SKIP_GIANT_ROWS = 4
+  FG_SPMM_SKIP_GIANT_ROWS = 4,
+  FG_SDDMM_TMA_STAGING = 8
 };
 int fg_next_launch_options(int32_t flags, int32_t max_ctas);
 
@@ -310,6 +318,13 @@ int fg_sddmm_coo_f32_host(const int32_t* row_dev, const int32_t* col_dev,
                           int64_t nnz, int64_t n_rows, int64_t n_cols,
                           int32_t feat_len, int32_t num_heads, int32_t device,
                           void* stream);
+
+/* Synchronises `device` and reads the status word of the SDDMM kernel that stages
+ * its tiles with TMA copies: 0 = fine; non-zero = a bounded wait for a copy gave up
+ * since the last call of this function (the function then returns FG_ERR_CUDA, the
+ * results of the edges behind that wait were not written, and the word is cleared).
+ * No counterpart in the reference (TVM kernels have no device-side waits). */
+int fg_sddmm_status(int32_t device, int32_t* device_status);
 
 /* Number of kernels one fg_sddmm_coo_f32 call launches for this shape. */
 int fg_sddmm_num_launches(int64_t nnz, int32_t feat_len, int32_t num_heads);

@@ -29,3 +29,11 @@ def bits(a):
     out = a.view(np.int32).copy()
     out[np.isnan(a)] = 0x7FC00000
     return out
+
+
+def row_classes(spmm_module):
+    """(giant, heavy, light) row counts of a built SpMM module's plan."""
+    import re
+    text = spmm_module.describe()
+    return tuple(int(re.search(r"%s: (\d+) rows" % k, text).group(1))
+                 for k in ("giant", "heavy", "light"))

@@ -10,7 +10,7 @@ import scipy.sparse as sp
 
 from featgraph_b200 import nd, te
 from featgraph_b200.module import VanillaSDDMMcuda, VanillaSpMMcuda
-from helpers import bits, features, random_csr
+from helpers import bits, features, random_csr, row_classes
 
 pytestmark = pytest.mark.gpu
 
@@ -38,7 +38,7 @@ def test_spmm_operator_pairs(oracle, msg_op, reduce_op):
         m.build([te.placeholder(x.shape)], {"msg_op": msg_op, "reduce_op": reduce_op},
                 {"heavy_row_threshold": threshold})
         if feat_len == 64:
-            assert m.num_launches() == 3                             # all three row classes
+            assert all(n > 0 for n in row_classes(m))                # all three row classes
         y = m.run([nd.array(x, m.ctx)]).asnumpy()
         want = oracle.gspmm_csr_f32(adj.indptr, adj.indices, adj.data, x, msg_op, reduce_op)
         assert np.array_equal(bits(want), bits(y)), (feat_len, threshold)

@@ -12,7 +12,7 @@ import torch
 from featgraph_b200 import _lib, graphs, nd, te
 from featgraph_b200.distributed import OverlappedPair, ShardedSDDMM, ShardedSpMM
 from featgraph_b200.module import VanillaSDDMMcuda, VanillaSpMMcuda
-from helpers import bits, features, random_csr
+from helpers import bits, features, random_csr, row_classes
 
 pytestmark = pytest.mark.gpu
 
@@ -25,7 +25,7 @@ def test_pair_on_one_gpu_equals_the_plain_calls(oracle):
     y2 = graphs.normal_features(g.n_cols, 64, graphs.FEAT2_SEED, dev)
     spmm = ShardedSpMM(adj, 64, dev)
     sddmm = ShardedSDDMM(g.coo_rows(), g.indices, g.n_rows, g.n_cols, 64, dev)
-    assert spmm.module.num_launches() == 3                 # giant rows exist: all phases run
+    assert all(n > 0 for n in row_classes(spmm.module))    # giant rows exist: all phases run
     pair = OverlappedPair(spmm, sddmm)
     assert pair.chained
     for _ in range(3):                                     # overlapping changes nothing

@@ -295,3 +295,41 @@ def test_multi_head_results_reach_an_unaligned_output(oracle):
                                                 140, 64, 8, 0, None))
         torch.cuda.synchronize()
         assert np.array_equal(bits(want).reshape(-1), bits(out.cpu().numpy()))
+
+
+@pytest.mark.parametrize("shape", [(32,), (64,), (256,), (4, 8), (8, 16), (2, 32), (2, 64)])
+def test_tma_staging_is_bit_identical(oracle, shape):
+    # the same tiles with the gathers handed to the tensor memory accelerator (tile::gather4
+    # copies, 128-byte swizzle, mbarriers): every head size the tile kernel has, row-sorted
+    # edges (staged dst runs) and a shuffled list (direct dst reads), ragged last tile
+    from featgraph_b200 import _lib
+    adj = random_csr(500, 400, 0.06, seed=91, dense_rows=(7, 300)).tocoo()
+    for shuffle in (False, True):
+        row, col = adj.row.astype(np.int32), adj.col.astype(np.int32)
+        if shuffle:
+            order = np.random.RandomState(92).permutation(row.shape[0])
+            row, col = row[order], col[order]
+        coo = sp.coo_matrix((np.ones(row.shape[0], np.float32), (row, col)), shape=adj.shape)
+        src = features((400,) + shape, seed=93)
+        dst = features((500,) + shape, seed=94)
+        m = VanillaSDDMMcuda(coo)
+        m.build([te.placeholder(src.shape), te.placeholder(dst.shape)], {}, {})
+        plain = m.run([nd.array(src, m.ctx), nd.array(dst, m.ctx)]).asnumpy().copy()
+        m.out_tvm.torch.zero_()
+        y = m.run([nd.array(src, m.ctx), nd.array(dst, m.ctx)],
+                  launch_flags=_lib.SDDMM_TMA_STAGING).asnumpy()
+        assert m.device_status() == 0
+        assert np.array_equal(bits(plain), bits(y))
+        heads = shape[0] if len(shape) == 2 else 1
+        want = oracle.sddmm_coo_f32(row, col, src.reshape(400, -1), dst.reshape(500, -1), heads)
+        assert np.array_equal(bits(want.reshape(y.shape)), bits(y))
+
+
+def test_tma_staging_refuses_what_it_does_not_cover():
+    from featgraph_b200 import _lib
+    adj = random_csr(50, 60, 0.1, seed=95).tocoo()
+    src, dst = features((60, 48), seed=96), features((50, 48), seed=97)
+    m = VanillaSDDMMcuda(adj)
+    m.build([te.placeholder(src.shape), te.placeholder(dst.shape)], {}, {"num_cuda_blocks": 64})
+    with pytest.raises(_lib.FeatGraphError):        # feat_len 48 runs the generic kernel
+        m.run([nd.array(src, m.ctx), nd.array(dst, m.ctx)], launch_flags=_lib.SDDMM_TMA_STAGING)

@@ -11,7 +11,7 @@ import torch
 import featgraph_b200 as fg
 from featgraph_b200 import _lib, graphs, nd, te
 from featgraph_b200.module import VanillaSpMMcuda
-from helpers import bits, features, random_csr
+from helpers import bits, features, random_csr, row_classes
 
 pytestmark = pytest.mark.gpu
 
@@ -49,7 +49,10 @@ def test_feature_lengths_and_both_row_paths(oracle, feat_len, threshold):
     assert not y[[0, 17, 299]].any()
     assert m.device_status() == 0
     if feat_len % 32 == 0 and threshold == 8:
-        assert m.num_launches() == 3          # light, heavy and giant kernels all ran
+        # the giant, heavy and light kernels, once per residency slab of the features
+        slab = 128 if feat_len % 128 == 0 else 64 if feat_len % 64 == 0 else 32
+        assert all(n > 0 for n in row_classes(m))
+        assert m.num_launches() == 3 * (feat_len // slab)
 
 
 @pytest.mark.parametrize("feat_len", [32, 64, 128])
@@ -65,7 +68,7 @@ def test_giant_rows_wrap_the_stage_ring(oracle, feat_len):
     x = features((3000, feat_len), seed=79)
     m, y = run_spmm(adj, x, {"heavy_row_threshold": 8})
     text = m.lower_to_ir([te.placeholder(x.shape)], {}, {"heavy_row_threshold": 8})
-    assert "giant: 0 rows" not in text and m.num_launches() == 3
+    assert "giant: 0 rows" not in text and all(n > 0 for n in row_classes(m))
     assert m.device_status() == 0
     assert np.array_equal(bits(oracle_spmm(oracle, adj, x)), bits(y))
 
@@ -183,7 +186,8 @@ def test_powerlaw_medium(oracle, feat_len):
     x = graphs.normal_features(20000, feat_len, graphs.FEAT_SEED, "cuda").cpu().numpy()
     m, y = run_spmm(adj, x)
     # light + heavy, and the giant class where the plan's time model makes the longest rows giant
-    assert m.num_launches() in (2, 3)
+    giant, heavy, light = row_classes(m)
+    assert heavy > 0 and light > 0
     assert m.device_status() == 0          # no bounded wait in the giant kernel gave up
     assert np.array_equal(bits(oracle_spmm(oracle, adj, x)), bits(y))
 

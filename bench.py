@@ -543,7 +543,7 @@ def run_gpu(args):
             "spmm": dict(roof(local_spmm_bytes, spmm_ms, traffic("spmm"),
                               spmm_l2_bytes(local_rows, spmm.local_nnz, FEAT)),
                          kernels="spmm_chain_kernel (giant rows) + spmm_heavy_kernel + spmm_light_kernel "
-                                 "(three concurrent streams)",
+                                 "(one stream, chained by programmatic dependent launches)",
                          gflops=round(2.0 * spmm.local_nnz * FEAT / (spmm_ms * 1e-3) / 1e9, 1),
                          gather_ms=round(float(phase_ms[1]), 4)),
             "sddmm": dict(roof(local_sddmm_bytes, sddmm_ms, traffic("sddmm"),

@@ -370,8 +370,8 @@ def run_gpu(args):
     spmm = ShardedSpMM(adj, FEAT, device, fused_gather=fused, peer_mode=args.peer_mode)
     sddmm = ShardedSDDMM(rows_dev, g.indices, n, g.n_cols, FEAT, device, fused_gather=fused,
                          peer_mode=args.peer_mode)
-    pair = OverlappedPair(spmm, sddmm)
-    overlap = args.schedule == "overlap" or (args.schedule == "auto" and world > 1)
+    pair = OverlappedPair(spmm, sddmm, order="split" if args.schedule == "split" else "chain")
+    overlap = args.schedule in ("overlap", "split") or (args.schedule == "auto" and world > 1)
     stream = torch.cuda.current_stream(device)
 
     def barrier():
@@ -562,9 +562,12 @@ def run_gpu(args):
             "parallelism": "spmm: nnz-balanced row blocks; sddmm: edge ranges; x%d; outputs "
                            "assembled by %s (spmm) / %s (sddmm); schedule: %s"
                            % (world, spmm.gather_mode, sddmm.gather_mode,
-                              "one chain of programmatic launches (SpMM, then the SDDMM dispatched "
-                              "under the tail of its giant rows) with one barrier pair per step; "
-                              "the per-kernel times come from a separate serial pass" if overlap else
+                              ("one chain of programmatic launches (%s) with one barrier pair per "
+                               "step; the per-kernel times come from a separate serial pass"
+                               % ("the SpMM's giant and heavy rows, the SDDMM, the SpMM's light rows"
+                                  if pair.order == "split" else
+                                  "SpMM, then the SDDMM dispatched under the tail of its giant rows"))
+                              if overlap else
                               "SpMM, then SDDMM, on one stream"),
             "e2e": {"value": round(e2e_value, 1), "unit": UNIT,
                     "h2d_bytes_per_step": int(3 * g.n_cols * FEAT * 4),
@@ -690,10 +693,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--peer-mode", choices=["auto", "store", "mcast", "push"], default="auto",
                     help="how results reach the peers (see featgraph_b200.distributed)")
-    ap.add_argument("--schedule", choices=["auto", "overlap", "serial"], default="auto",
+    ap.add_argument("--schedule", choices=["auto", "overlap", "split", "serial"], default="auto",
                     help="serial: SpMM then SDDMM; overlap: the two side by side in one chain of "
-                         "programmatic launches (OverlappedPair); auto: serial on one GPU (where "
-                         "overlapping gains nothing), overlap on several")
+                         "programmatic launches (OverlappedPair); split: the same chain with the "
+                         "SDDMM between the SpMM's long rows and its light rows; auto: serial on "
+                         "one GPU (where overlapping gains nothing), overlap on several")
     ap.add_argument("--no-l2-probe", action="store_true",
                     help="skip the measurement of the L2 gather peak (roofline_l2)")
     ap.add_argument("--nccl-gather", action="store_true",

@@ -32,9 +32,11 @@ LaunchOptions take_launch_options() {
 
 extern "C" int fg_next_launch_options(int32_t flags, int32_t max_ctas) {
   const int32_t known = FG_LAUNCH_PROGRAMMATIC | FG_SPMM_GIANT_ROWS_ONLY |
-                        FG_SPMM_SKIP_GIANT_ROWS | FG_SDDMM_TMA_STAGING;
-  if ((flags & ~known) != 0 || max_ctas < 0 ||
-      ((flags & FG_SPMM_GIANT_ROWS_ONLY) && (flags & FG_SPMM_SKIP_GIANT_ROWS)))
+                        FG_SPMM_SKIP_GIANT_ROWS | FG_SDDMM_TMA_STAGING | FG_SPMM_LONG_ROWS_ONLY |
+                        FG_SPMM_SKIP_LONG_ROWS;
+  const int32_t cuts = flags & (FG_SPMM_GIANT_ROWS_ONLY | FG_SPMM_SKIP_GIANT_ROWS |
+                                FG_SPMM_LONG_ROWS_ONLY | FG_SPMM_SKIP_LONG_ROWS);
+  if ((flags & ~known) != 0 || max_ctas < 0 || (cuts & (cuts - 1)) != 0)  // at most one cut
     return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad launch options: flags=%d max_ctas=%d", (int)flags,
                     (int)max_ctas);
   fg::g_next_options.flags = flags;

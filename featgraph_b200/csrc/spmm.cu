@@ -1097,8 +1097,10 @@ static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const i
   // `any`: the next launch of this call may be programmatic -- because the call itself is
   // (the caller's assertion), or because a kernel of this call is already in the stream
   bool any = (opt.flags & FG_LAUNCH_PROGRAMMATIC) != 0;
-  const bool giants = (opt.flags & FG_SPMM_SKIP_GIANT_ROWS) == 0;
-  const bool rest = (opt.flags & FG_SPMM_GIANT_ROWS_ONLY) == 0;
+  // which row classes this call serves (the cuts of fg_launch_flags)
+  const bool giants = (opt.flags & (FG_SPMM_SKIP_GIANT_ROWS | FG_SPMM_SKIP_LONG_ROWS)) == 0;
+  const bool heavies = (opt.flags & (FG_SPMM_GIANT_ROWS_ONLY | FG_SPMM_SKIP_LONG_ROWS)) == 0;
+  const bool rest = (opt.flags & (FG_SPMM_GIANT_ROWS_ONLY | FG_SPMM_LONG_ROWS_ONLY)) == 0;
   if (!p->vector_ok || !aligned) {  // no row classes here: the whole SpMM is "the rest"
     if (!rest) return FG_OK;
     const long long grid = (p->n_rows + 7) / 8;
@@ -1136,14 +1138,13 @@ static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const i
                                                       p->n_giant, width, st, any)));
       any = true;
     }
-    if (!rest) continue;
-    if (p->n_heavy > 0) {
+    if (heavies && p->n_heavy > 0) {
       FG_CUDA_TRY((p->heavy_vec == 2
                        ? launch_heavy<2, MSG, RED>(p, indptr, indices, vals, xs, ys, width, st, any)
                        : launch_heavy<1, MSG, RED>(p, indptr, indices, vals, xs, ys, width, st, any)));
       any = true;
     }
-    if (p->n_light > 0) {
+    if (rest && p->n_light > 0) {
       const int first = p->n_giant + p->n_heavy;
       cudaError_t e;
       switch (p->slab_w) {

@@ -458,7 +458,12 @@ class OverlappedPair(object):
     so that both are resident at once (1.65 to 1.97: the SDDMM needs its full occupancy).
     """
 
-    def __init__(self, spmm, sddmm):
+    def __init__(self, spmm, sddmm, order="chain"):
+        """order: "chain" -- the SpMM, then the SDDMM behind it; "split" -- the SpMM's long
+        rows (giant and heavy: the dependent chains), the SDDMM, then the SpMM's light rows,
+        so that the SDDMM's results start crossing NVLink at once."""
+        assert order in ("chain", "split")
+        self.order = order
         self.spmm, self.sddmm = spmm, sddmm
         self.device = spmm.device
         self.fused = spmm._symm is not None and sddmm._symm is not None
@@ -470,12 +475,18 @@ class OverlappedPair(object):
         spmm, sddmm = self.spmm, self.sddmm
         if self.fused:
             spmm._sync.barrier()
-        spmm.launch_local(x)
+        split = self.order == "split" and self.chained
+        if split:
+            spmm.module.run([x], launch_flags=_lib.SPMM_LONG_ROWS_ONLY)
+        else:
+            spmm.launch_local(x)
         if sddmm.edge_hi > sddmm.edge_lo:
             if self.chained:
                 sddmm.module.run([src, dst], launch_flags=_lib.LAUNCH_PROGRAMMATIC)
             else:
                 sddmm.launch_local(src, dst)
+        if split:
+            spmm.module.run([x], launch_flags=_lib.SPMM_SKIP_LONG_ROWS | _lib.LAUNCH_PROGRAMMATIC)
         if self.fused:
             spmm._sync.barrier()
         elif spmm.world > 1:

@@ -69,6 +69,9 @@ const char* fg_version(void);
  *   for the grid before it, so a later, ordinary launch still sees all of them complete.
  * FG_SPMM_GIANT_ROWS_ONLY / FG_SPMM_SKIP_GIANT_ROWS: the SpMM call computes only the
  *   plan's giant rows / everything but them; the two calls together are one SpMM.
+ * FG_SPMM_LONG_ROWS_ONLY / FG_SPMM_SKIP_LONG_ROWS: the same cut one class further down:
+ *   the giant AND the heavy rows (every row that is one long dependent chain) / the light
+ *   rows only.
  * max_ctas > 0 (SDDMM): at most this many CTAs, each walking more edges, so that the whole
  *   grid is resident at once and the kernel behind it can be dispatched beside it.
  * FG_SDDMM_TMA_STAGING (SDDMM, multiply / sum, feat_len a multiple of 32): the gathered
@@ -83,7 +86,9 @@ enum fg_launch_flags {
   FG_LAUNCH_PROGRAMMATIC = 1,
   FG_SPMM_GIANT_ROWS_ONLY = 2,
   FG_SPMM_SKIP_GIANT_ROWS = 4,
-  FG_SDDMM_TMA_STAGING = 8
+  FG_SDDMM_TMA_STAGING = 8,
+  FG_SPMM_LONG_ROWS_ONLY = 16,
+  FG_SPMM_SKIP_LONG_ROWS = 32
 };
 int fg_next_launch_options(int32_t flags, int32_t max_ctas);
 

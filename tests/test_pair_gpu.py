@@ -62,6 +62,13 @@ def test_spmm_in_two_phases_and_bounded_sddmm_grids(oracle):
             assert np.isnan(y).all()                         # the generic kernel has no classes
         y = m.run([xd], launch_flags=_lib.SPMM_SKIP_GIANT_ROWS | _lib.LAUNCH_PROGRAMMATIC).asnumpy()
         assert np.array_equal(want, bits(y))
+        # the same cut one class further down: giant and heavy rows, then the light rows
+        long_rows = np.diff(adj.indptr) > max(threshold, 1) if feat_len == 64 else giant & False
+        m.out_tvm.torch.fill_(float("nan"))
+        y = m.run([xd], launch_flags=_lib.SPMM_LONG_ROWS_ONLY).asnumpy()
+        assert np.array_equal(want[long_rows], bits(y)[long_rows]) and np.isnan(y[~long_rows]).all()
+        y = m.run([xd], launch_flags=_lib.SPMM_SKIP_LONG_ROWS | _lib.LAUNCH_PROGRAMMATIC).asnumpy()
+        assert np.array_equal(want, bits(y))
     coo = random_csr(700, 600, 0.05, seed=80).tocoo()
     src, dst = features((600, 4, 16), seed=81), features((700, 4, 16), seed=82)
     want = oracle.sddmm_coo_f32(coo.row, coo.col, src, dst, num_heads=4)
@@ -73,6 +80,7 @@ def test_spmm_in_two_phases_and_bounded_sddmm_grids(oracle):
                     launch_flags=_lib.LAUNCH_PROGRAMMATIC, max_ctas=max_ctas).asnumpy()
         assert np.array_equal(bits(want), bits(out)), max_ctas
     lib = _lib.load()
-    assert lib.fg_next_launch_options(8, 0) == 1 and lib.fg_next_launch_options(6, 0) == 1
+    assert lib.fg_next_launch_options(64, 0) == 1 and lib.fg_next_launch_options(6, 0) == 1
+    assert lib.fg_next_launch_options(16 | 32, 0) == 1 and lib.fg_next_launch_options(2 | 32, 0) == 1
     assert lib.fg_next_launch_options(0, -1) == 1
     assert lib.fg_next_launch_options(1, 5) == 0 and lib.fg_next_launch_options(0, 0) == 0

@@ -24,7 +24,7 @@ import os
 import numpy as np
 import torch
 
-from . import graphs
+from . import _lib, graphs
 from .distributed import ShardedSDDMM, ShardedSpMM
 
 NOMINAL_HBM_GBS = 8000.0
@@ -98,6 +98,9 @@ def main(argv=None):
     ap.add_argument("--col-partitions", type=int, default=1,
                     help="SpMM (one GPU): the reference's 1-D source-vertex partitioning, "
                          "VanillaSpMMx86's num_col_partitions; SDDMM: see --row-partitions")
+    ap.add_argument("--sddmm-tma", action="store_true",
+                    help="SDDMM: stage the tiles with TMA tile::gather4 copies "
+                         "(FG_SDDMM_TMA_STAGING) instead of cp.async")
     ap.add_argument("--sweep", action="store_true",
                     help="run the whole configured sweep in one process: SpMM and SDDMM at feat-len "
                          "32 ... 512, then multi-head SDDMM (4,16), (8,32), (16,64)")
@@ -167,6 +170,8 @@ def main(argv=None):
             nnz = nnz_sd
             y2 = graphs.normal_features(g.n_rows, shape, graphs.FEAT2_SEED, device)
             op = ShardedSDDMM(rows, cols, n, g.n_cols, shape, device, peer_mode=args.peer_mode)
+            if args.sddmm_tma:
+                op.module.default_launch_flags = _lib.SDDMM_TMA_STAGING
             call = lambda: op.run(x, y2)                   # noqa: E731
             alg = 8 * nnz + 8 * nnz * f + 4 * nnz * heads
         for _ in range(3):

@@ -32,7 +32,6 @@
 // Every kernel is a template over a message operator and a reducer (common.cuh); multiply
 // with sum is the reference's SpMM, the other pairs are the generalised form.
 #include <algorithm>
-#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -330,11 +329,7 @@ struct ChainShape {
   static_assert(PRODUCERS == (RETIRE ? WARPS - 1 - (WARPS - 1) / 4 : WARPS - 1), "producer count");
 };
 // The giant rows: a whole SM per (row, 32-float slab), nine producers, a 48-block ring.
-#ifndef FG_GT_GROUP
-#define FG_GT_GROUP 16
-#define FG_GT_GROUPS 3
-#endif
-using GiantShape = ChainShape<12, 9, FG_GT_GROUP, FG_GT_GROUPS, true, 1>;
+using GiantShape = ChainShape<12, 9, 16, 3, true, 1>;
 // Smaller shapes (4 to 6 warps, rings of 16 to 32 blocks, two or three CTAs per SM) were
 // built and measured as the kernel of the heavy class: one 30 000-nonzero row alone walks
 // at 7.5 to 9.4 cycles per nonzero (the single-warp cp.async kernel: 24 alone, 45 beside
@@ -549,11 +544,7 @@ spmm_chain_kernel(const int* __restrict__ indptr, const int* __restrict__ indice
   // check, so that the check costs a compare; the fence behind a successful check
   // turns it into an acquire (every lane's loads of the block come after it).  A lane
   // whose bounded wait gives up only notes it; the warp looks at the notes at the end.
-#if defined(FG_GT_DIAG)
-  auto peek = [&](int j) { return (unsigned)j + 1u; };  // timing diagnosis only: no flag loads
-#else
   auto peek = [&](int j) { return ld_relaxed_shared(&ready[j % kGtRing]); };
-#endif
   bool gave_up = false;
   auto await = [&](int j, unsigned seen) {
     const unsigned want = (unsigned)j + 1u;
@@ -721,7 +712,6 @@ struct fg_spmm_plan {
   int* status_dev = nullptr;  // set by a giant-kernel wait that gave up
   unsigned poll_limit = 0;    // polls a chain-kernel wait makes before it gives up
   int l2_bytes = 0, n_sms = 0;
-  bool slabs_together = false;  // one launch per class over all slabs (experiments only)
 };
 
 namespace fg {
@@ -847,23 +837,15 @@ static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, in
   p->heavy_vec = (p->slab_w % 64 == 0) ? 2 : 1;
   {
     // Giant class: the rows whose add chain, walked by the heavy kernel's single warp,
-    // would last more than kGiantShareOfCall of the call.  The call is estimated as the longer of
+    // would last more than kGiantShareOfCall of a trio (the three kernels' pass over one
+    // residency slab).  The trio is estimated as the longer of
     // its throughput time and the longest row's chain in the giant kernel; a shard of
     // a multi-GPU run has less of the former, so more of its rows turn giant.  The
     // giant kernel gives an SM to 32 floats of one row, so it is kept for such rows.
-    double light_div = kLightCyclesPerNnzOfPass, giant_share = kGiantShareOfCall;
-#ifdef FG_TUNING
-    if (const char* e = getenv("FG_LIGHT_DIV")) light_div = atof(e);
-    if (const char* e = getenv("FG_GIANT_FRAC")) giant_share = atof(e);
-    if (const char* e = getenv("FG_SLABS_TOGETHER")) p->slabs_together = atoi(e) != 0;
-#endif
-    // the floats of a row that one giant / heavy / light trio covers: the residency slab
-    const int width = p->slabs_together ? feat_len : p->slab_w;
-    const double t_throughput = (double)p->nnz * (width / 32.0) * kCyclesPerNnzSlab * 148.0 /
+    // (one giant / heavy / light trio covers one residency slab of every row: slab_w floats)
+    const double t_throughput = (double)p->nnz * (p->slab_w / 32.0) * kCyclesPerNnzSlab * 148.0 /
                                 std::max(1, p->n_sms);
     const double t_call = std::max(t_throughput, (double)max_deg * kGiantCyclesPerNnz);
-    // a light row has to fit the pass over one residency slab
-    const double t_pass = t_call * p->slab_w / width;
     // Heavy class: the light kernel moves about twice the nonzeros per SM-cycle of the heavy
     // one (its gathers go straight to registers; the heavy and giant kernels pass every
     // gathered byte through shared memory) but walks a row at about one gather latency per 8
@@ -874,8 +856,8 @@ static int plan_create(const int32_t* indptr, int64_t n_rows, int64_t n_cols, in
     // 11289 / 28824: 1.98, 15052 / 38432: 2.12, 22579 / 57648: 2.56.
     if (heavy_threshold <= 0)
       p->heavy_threshold = (int)std::min<double>(
-          1 << 20, std::max<double>(kDefaultHeavyThreshold, t_pass / light_div));
-    const double by_time = giant_share * t_call / kHeavyCyclesPerNnz;
+          1 << 20, std::max<double>(kDefaultHeavyThreshold, t_call / kLightCyclesPerNnzOfPass));
+    const double by_time = kGiantShareOfCall * t_call / kHeavyCyclesPerNnz;
     int64_t thr = (int64_t)std::min(by_time, 1e9);
     thr = std::max<int64_t>(thr, kMinGiantThreshold);
     // an explicit heavy threshold (tests use tiny ones) scales the giant class down with it
@@ -973,7 +955,7 @@ extern "C" int fg_spmm_plan_set_poll_limit(fg_spmm_plan* p, int64_t polls) {
 extern "C" int fg_spmm_plan_num_launches(const fg_spmm_plan* p) {
   if (!p || p->n_rows == 0) return 0;
   if (!p->vector_ok) return 1;
-  const int trios = p->slabs_together ? 1 : p->feat_len / p->slab_w;
+  const int trios = p->feat_len / p->slab_w;
   return trios * ((p->n_giant > 0 ? 1 : 0) + (p->n_heavy > 0 ? 1 : 0) + (p->n_light > 0 ? 1 : 0));
 }
 
@@ -983,7 +965,7 @@ extern "C" int fg_spmm_plan_describe(const fg_spmm_plan* p, char* buf, int64_t b
   if (p->vector_ok) {
     const int G = p->slab_w / 4;
     // grids of ONE trio: the kernels run once per residency slab of the features
-    const int width = p->slabs_together ? p->feat_len : p->slab_w;
+    const int width = p->slab_w;
     const int hv_slabs = width / (32 * p->heavy_vec);
     const long long light_items = (long long)p->n_light * (width / p->slab_w);
     snprintf(buf, (size_t)buf_len,
@@ -1124,12 +1106,8 @@ static int spmm_launch_ops(const fg_spmm_plan* p, const int32_t* indptr, const i
   // gather from the SAME slab of X.  In one launch over all slabs each kernel walks the
   // slabs at its own pace, two or three slabs are live at a time, and together they no
   // longer fit L2.
-  const int width = p->slabs_together ? p->feat_len : p->slab_w;
-  int f_end = p->feat_len;
-#ifdef FG_TUNING
-  if (const char* e = getenv("FG_FIRST_TRIOS")) f_end = std::min(f_end, atoi(e) * width);
-#endif
-  for (int f0 = 0; f0 < f_end; f0 += width) {
+  const int width = p->slab_w;
+  for (int f0 = 0; f0 < p->feat_len; f0 += width) {
     const float* xs = x + f0;
     OutPtrs ys = y;
     for (int q = 0; q < ys.n; ++q) ys.p[q] += f0;

@@ -434,9 +434,10 @@ class ShardedSDDMM(_Sharded):
         return out_host
 
     def device_status(self):
+        """Raises if a bounded device-side wait gave up (peer barrier, TMA staging); else 0."""
         if self._sync is not None:
             self._sync.check()
-        return 0
+        return self.module.device_status() if hasattr(self, "module") else 0
 
     def num_launches(self):
         return self.module.num_launches() if hasattr(self, "module") else 0

@@ -188,13 +188,14 @@ class SDDMMbase(object):
         ``self.out_tvm``, the same array every call (sddmm.py:115-129).  ``launch_flags`` /
         ``max_ctas`` (additions): fg_next_launch_options for this call."""
         src, dst = self._checked_inputs(input_tvm_ndarrays)
-        self._launch(src, dst, launch_flags, max_ctas)
+        self._launch(src, dst, launch_flags | getattr(self, "default_launch_flags", 0), max_ctas)
         return self.out_tvm
 
     def measure_average_time(self, input_tvm_ndarrays, num_runs):
         """Mean kernel time in seconds over ``num_runs`` launches (sddmm.py:131-150)."""
         src, dst = self._checked_inputs(input_tvm_ndarrays)
-        return time_launches(self._ctx, lambda: self._launch(src, dst), num_runs)
+        flags = getattr(self, "default_launch_flags", 0)
+        return time_launches(self._ctx, lambda: self._launch(src, dst, flags), num_runs)
 
     def run_host(self, src_host, dst_host, out_host):
         """End-to-end call on HOST buffers (ideally pinned): uploads both feature arrays,

@@ -10,6 +10,7 @@ entry points release the interpreter lock while they wait, which is what lets tw
 threads do this.
 """
 import threading
+import time
 
 import torch
 
@@ -26,8 +27,10 @@ class HostPair(object):
         self.streams = (torch.cuda.Stream(device=self.device),
                         torch.cuda.Stream(device=self.device))
 
-    def _call(self, which, fn, args, errors):
+    def _call(self, which, fn, args, errors, delay=0.0):
         try:
+            if delay:
+                time.sleep(delay)
             torch.cuda.set_device(self.device)
             with torch.cuda.stream(self.streams[which]):
                 fn(*args)
@@ -39,10 +42,13 @@ class HostPair(object):
         for s in self.streams:
             s.wait_stream(main)
         errors = []
+        # The SDDMM call is the longer chain (two uploads, then a result of 4 bytes per edge to
+        # bring back), so it is issued from this thread, at once: its uploads reach the copy
+        # engine ahead of the SpMM's, whose thread holds its call back for a moment.
         t = threading.Thread(target=self._call,
-                             args=(1, self.sddmm.run_host, (src_host, dst_host, out_host), errors))
+                             args=(0, self.spmm.run_host, (x_host, y_host), errors, 3e-4))
         t.start()
-        self._call(0, self.spmm.run_host, (x_host, y_host), errors)
+        self._call(1, self.sddmm.run_host, (src_host, dst_host, out_host), errors)
         t.join()
         for s in self.streams:
             main.wait_stream(s)

@@ -99,8 +99,9 @@ int fg_next_launch_options(int32_t flags, int32_t max_ctas);
  * single-warp CTAs, the few giant rows by producer/consumer CTAs), the
  * feature-slab width chosen from the device's L2 size, and the status word of
  * the giant-row kernel's bounded waits.  A call launches its (up to three)
- * kernels back to back on the caller's stream; the plan is read-only during a
- * call apart from that status word, which all calls of one plan share. */
+ * kernels back to back on the caller's stream, once per feature slab when
+ * feat_len is wider than the slab; the plan is read-only during a call apart
+ * from that status word, which all calls of one plan share. */
 typedef struct fg_spmm_plan fg_spmm_plan;
 
 /* Builds the plan from the HOST copy of indptr (n_rows + 1 int32 entries).

@@ -32,7 +32,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from featgraph_b200 import graphs  # noqa: E402
+from featgraph_b200 import _lib, graphs  # noqa: E402
 
 FEAT = 64
 METRIC = "spmm_plus_sddmm_fp32_feat64_gflops"
@@ -548,7 +548,9 @@ def run_gpu(args):
                          gather_ms=round(float(phase_ms[1]), 4)),
             "sddmm": dict(roof(local_sddmm_bytes, sddmm_ms, traffic("sddmm"),
                                sddmm_l2_bytes(n, local_edges, FEAT)),
-                          kernels="sddmm_tile_kernel",
+                          kernels=("sddmm_rowreg_kernel (dst operand in registers)"
+                                   if getattr(getattr(sddmm, "module", None), "default_launch_flags", 0)
+                                   & _lib.SDDMM_ROW_REGISTERS else "sddmm_tile_kernel"),
                           gflops=round(2.0 * local_edges * FEAT / (sddmm_ms * 1e-3) / 1e9, 1),
                           gather_ms=round(float(phase_ms[3]), 4)),
         }

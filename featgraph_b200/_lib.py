@@ -38,7 +38,7 @@ EXPORTED_SYMBOLS = (
 )
 
 LAUNCH_PROGRAMMATIC, SPMM_GIANT_ROWS_ONLY, SPMM_SKIP_GIANT_ROWS, SDDMM_TMA_STAGING = 1, 2, 4, 8  # fg_launch_flags
-SPMM_LONG_ROWS_ONLY, SPMM_SKIP_LONG_ROWS = 16, 32
+SPMM_LONG_ROWS_ONLY, SPMM_SKIP_LONG_ROWS, SDDMM_ROW_REGISTERS = 16, 32, 64
 MSG_OPS = ("mul", "add", "sub", "div", "copy_lhs", "copy_rhs")    # enum fg_msg_op
 REDUCE_OPS = ("sum", "max", "min")                                # enum fg_reduce_op
 

@@ -33,7 +33,7 @@ LaunchOptions take_launch_options() {
 extern "C" int fg_next_launch_options(int32_t flags, int32_t max_ctas) {
   const int32_t known = FG_LAUNCH_PROGRAMMATIC | FG_SPMM_GIANT_ROWS_ONLY |
                         FG_SPMM_SKIP_GIANT_ROWS | FG_SDDMM_TMA_STAGING | FG_SPMM_LONG_ROWS_ONLY |
-                        FG_SPMM_SKIP_LONG_ROWS;
+                        FG_SPMM_SKIP_LONG_ROWS | FG_SDDMM_ROW_REGISTERS;
   const int32_t cuts = flags & (FG_SPMM_GIANT_ROWS_ONLY | FG_SPMM_SKIP_GIANT_ROWS |
                                 FG_SPMM_LONG_ROWS_ONLY | FG_SPMM_SKIP_LONG_ROWS);
   if ((flags & ~known) != 0 || max_ctas < 0 || (cuts & (cuts - 1)) != 0)  // at most one cut

@@ -41,6 +41,7 @@ constexpr int kSdWarpFloats = kSdStages * kSdStageFloats;
 constexpr int kSdSmemBytes = kSdWarps * kSdWarpFloats * 4;
 static_assert(kSdStageFloats % 4 == 0, "stages stay 16-byte aligned");
 
+constexpr int kSdTilesPerWarpConst = 16;             // tiles a warp walks (kSdTilesPerWarp)
 constexpr int kSdLanesPerSeg = kSdChunk / 4;          // 16-byte copies per row segment
 constexpr int kSdRowsPerCopy = 32 / kSdLanesPerSeg;   // segments one warp-wide copy covers
 
@@ -216,6 +217,158 @@ sddmm_tile_kernel(const int* __restrict__ row, const int* __restrict__ col,
   // If this grid was dispatched behind another one without waiting for it (programmatic
   // launch), its last CTA stays until that one has completed: "this grid is complete" then
   // covers both for whatever follows in the stream.
+  if (blockIdx.x == gridDim.x - 1 && warp == 0) wait_for_prior_grids();
+}
+
+// ---- single-head tiles with the dst operand in registers -----------------------------
+//
+// sddmm_rowreg_kernel (one head, feat_len a multiple of 32).  In sddmm_tile_kernel a lane
+// fetches BOTH operands of its edge through the LSU: per 32-edge x 32-float stage the
+// lanes' loads of the dst segment cost as many shared-memory wavefronts as the loads of
+// their own src row (a 16-byte load returns 512 bytes to the warp even when every lane
+// reads the same address), 67 of the stage's 96, and that pipe is what bounds the kernel
+// (84 % busy).  A row-sorted edge list repeats dst[row] for hundreds of consecutive edges,
+// so here the dst segment lives in REGISTERS: a warp takes its tiles four at a time, walks
+// the feature axis in the OUTER loop and the four tiles in the inner one, and loads the 32
+// floats of dst[row] for the current chunk once per group of tiles whose edges all share
+// that row (eight 16-byte loads with one address).  The four partial sums wait in
+// registers for the next chunk; the order of the additions per edge is unchanged (k
+// ascending), so the results are sddmm_tile_kernel's bit for bit.  A tile that crosses a
+// row boundary reads its lanes' dst segments from global memory (L1) instead.
+// Two stages per warp: the copies of the next (tile, chunk) are in flight while the
+// current one is summed.
+// Measured on B200 (114.6 M edges, feat_len 64, ms; sddmm_tile_kernel: 2.82): 4 warps x 4
+// CTAs per SM (128 registers), groups of 4 tiles, 2 stages: 2.64; 5 CTAs (96 registers, a few
+// spills): 2.65; 6 CTAs (80 registers): 3.37; 3 stages: 2.74; 6 warps x 3 CTAs: 2.70; groups
+// of 8 tiles: 3.10; L1-allocating copies (.ca): 2.74 (better only from feat_len 256 up).
+constexpr int kRrWarps = 4;
+constexpr int kRrMinCtas = 4;
+constexpr int kRrTiles = 4;              // tiles per group (partial sums held in registers)
+constexpr int kRrStages = 2;
+constexpr int kRrAhead = kRrStages - 1;  // stages in flight beyond the one being summed
+static_assert(kRrAhead >= 1 && kRrAhead <= kRrTiles, "prefetch distance");
+constexpr int kRrStageFloats = 32 * kSdPitch;
+constexpr int kRrSmemBytes = kRrWarps * kRrStages * kRrStageFloats * 4;
+static_assert(kSdTilesPerWarpConst % kRrTiles == 0, "a warp's tiles split into whole groups");
+
+template <int MSG, int RED>
+__global__ void __launch_bounds__(kRrWarps * 32, kRrMinCtas)
+sddmm_rowreg_kernel(const int* __restrict__ row, const int* __restrict__ col,
+                    const float* __restrict__ src, const float* __restrict__ dst,
+                    const __grid_constant__ OutPtrs out, long long nnz, int F,
+                    int tiles_per_warp) {
+  constexpr unsigned kFull = 0xffffffffu;
+  extern __shared__ __align__(16) float rr_smem[];
+  launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  float* wbuf = rr_smem + warp * kRrStages * kRrStageFloats;
+
+  const long long n_tiles = (nnz + 31) / 32;
+  const long long tile0 = ((long long)blockIdx.x * kRrWarps + warp) * tiles_per_warp;
+  if (tile0 >= n_tiles) return;  // (warp 0 of every CTA has tiles)
+  const int n_chunks = F / kSdChunk;
+  const int part = (lane % kSdLanesPerSeg) * 4;
+  const int e_lo = lane / kSdLanesPerSeg;
+
+  // tiles past the end of the list are walked as empty ones (indices 0, nothing stored),
+  // so that every group is whole
+  for (int g0 = 0; g0 < tiles_per_warp && tile0 + g0 < n_tiles; g0 += kRrTiles) {
+    int cidx[kRrTiles], ridx[kRrTiles], row0[kRrTiles];
+    bool one_run[kRrTiles];
+    float acc[kRrTiles];
+#pragma unroll
+    for (int j = 0; j < kRrTiles; ++j) {
+      const long long e = (tile0 + g0 + j) * 32 + lane;
+      cidx[j] = 0;
+      ridx[j] = 0;
+      if (e < nnz) {
+        ridx[j] = ld_stream(row + e);
+        cidx[j] = ld_stream(col + e);
+      }
+      acc[j] = red_identity<RED>();
+    }
+#pragma unroll
+    for (int j = 0; j < kRrTiles; ++j) {
+      row0[j] = __shfl_sync(kFull, ridx[j], 0);
+      one_run[j] = __all_sync(kFull, ridx[j] == row0[j]);
+    }
+    // copies of (tile j, chunk ch) into stage buffer `buf`
+    auto issue = [&](int cj, int ch, int buf) {
+      float* sbuf = wbuf + buf * kRrStageFloats;
+      const float* sp = src + (size_t)ch * kSdChunk + part;
+#pragma unroll
+      for (int k = 0; k < 32 / kSdRowsPerCopy; ++k) {
+        const int e = e_lo + kSdRowsPerCopy * k;
+        const int c = __shfl_sync(kFull, cj, e);
+        cp_async16_cg(sbuf + e * kSdPitch + part, sp + (size_t)c * F);
+      }
+      cp_async_commit();
+    };
+#pragma unroll
+    for (int j = 0; j < kRrAhead; ++j) issue(cidx[j], 0, j);
+    int buf = 0;
+    for (int ch = 0; ch < n_chunks; ++ch) {
+      float4 b[kSdChunk / 4];
+      int have_row = -1;
+#pragma unroll
+      for (int j = 0; j < kRrTiles; ++j) {
+        // the stage kRrAhead ahead of this one, if the group has it: tile (j + kRrAhead) mod
+        // kRrTiles of this chunk or of the next
+        {
+          const int jn = (j + kRrAhead) % kRrTiles;
+          const int chn = ch + (j + kRrAhead) / kRrTiles;
+          int buf_n = buf + kRrAhead;
+          if (buf_n >= kRrStages) buf_n -= kRrStages;
+          if (chn < n_chunks)
+            issue(cidx[jn], chn, buf_n);
+          else
+            cp_async_commit();  // an empty group keeps the wait below uniform
+        }
+        if (one_run[j] && row0[j] != have_row) {
+          const float4* d4 = reinterpret_cast<const float4*>(dst + (size_t)row0[j] * F +
+                                                            (size_t)ch * kSdChunk);
+#pragma unroll
+          for (int q = 0; q < kSdChunk / 4; ++q) b[q] = __ldg(d4 + q);
+          have_row = row0[j];
+        }
+        cp_async_wait<kRrAhead>();
+        __syncwarp();
+        const float4* s4 =
+            reinterpret_cast<const float4*>(wbuf + buf * kRrStageFloats + lane * kSdPitch);
+        if (one_run[j]) {
+#pragma unroll
+          for (int q = 0; q < kSdChunk / 4; ++q) {
+            const float4 a = s4[q];
+            acc[j] = combine<MSG, RED>(acc[j], a.x, b[q].x);
+            acc[j] = combine<MSG, RED>(acc[j], a.y, b[q].y);
+            acc[j] = combine<MSG, RED>(acc[j], a.z, b[q].z);
+            acc[j] = combine<MSG, RED>(acc[j], a.w, b[q].w);
+          }
+        } else {
+          const float4* d4 = reinterpret_cast<const float4*>(dst + (size_t)ridx[j] * F +
+                                                            (size_t)ch * kSdChunk);
+#pragma unroll
+          for (int q = 0; q < kSdChunk / 4; ++q) {
+            const float4 a = s4[q];
+            const float4 d = __ldg(d4 + q);
+            acc[j] = combine<MSG, RED>(acc[j], a.x, d.x);
+            acc[j] = combine<MSG, RED>(acc[j], a.y, d.y);
+            acc[j] = combine<MSG, RED>(acc[j], a.z, d.z);
+            acc[j] = combine<MSG, RED>(acc[j], a.w, d.w);
+          }
+        }
+        __syncwarp();  // every lane is done with this buffer before it is refilled
+        if (++buf == kRrStages) buf = 0;
+      }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int j = 0; j < kRrTiles; ++j) {
+      const long long e = (tile0 + g0 + j) * 32 + lane;
+      if (e < nnz) out_store(out, (size_t)e, acc[j]);
+    }
+  }
   if (blockIdx.x == gridDim.x - 1 && warp == 0) wait_for_prior_grids();
 }
 
@@ -498,7 +651,7 @@ sddmm_generic_kernel(const int* __restrict__ row, const int* __restrict__ col,
   out_store(out, (size_t)i, acc);
 }
 
-constexpr int kSdTilesPerWarp = 16;
+constexpr int kSdTilesPerWarp = kSdTilesPerWarpConst;
 
 // -1 -> generic kernel; otherwise the HEAD_DIM template argument of the tile kernel.
 static int sddmm_variant(int F, int H) {
@@ -664,7 +817,8 @@ static cudaError_t sddmm_launch_kernels(int variant, long long grid, int tiles_p
                                         const int32_t* col, const float* src, const float* dst,
                                         const OutPtrs& out, int64_t nnz, int64_t n_rows,
                                         int64_t n_cols, int32_t feat_len, int32_t num_heads,
-                                        int32_t device, cudaStream_t st, bool tma) {
+                                        int32_t device, cudaStream_t st, bool tma,
+                                        bool rowreg = false) {
   // heads leave four at a time where the lane's four results are one aligned 16-byte piece
   int vec_heads = num_heads % 4 == 0;
   for (int q = 0; q < out.n; ++q)
@@ -672,6 +826,18 @@ static cudaError_t sddmm_launch_kernels(int variant, long long grid, int tiles_p
   if (variant < 0)
     return launch_kernel(sddmm_generic_kernel<MSG, RED>, (unsigned)grid, 256, 0, st, programmatic,
                          row, col, src, dst, out, (long long)nnz * num_heads, feat_len, num_heads);
+  if (rowreg) {
+    static thread_local int configured_dev = -1;
+    if (configured_dev != device) {
+      cudaError_t e = cudaFuncSetAttribute(sddmm_rowreg_kernel<MSG, RED>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kRrSmemBytes);
+      if (e != cudaSuccess) return e;
+      configured_dev = device;
+    }
+    return launch_kernel(sddmm_rowreg_kernel<MSG, RED>, (unsigned)grid, kRrWarps * 32, kRrSmemBytes,
+                         st, programmatic, row, col, src, dst, out, (long long)nnz, feat_len,
+                         tiles_per_warp);
+  }
   if (tma && !(MSG == FG_MSG_MUL && RED == FG_REDUCE_SUM)) return cudaErrorNotSupported;
   if constexpr (MSG == FG_MSG_MUL && RED == FG_REDUCE_SUM) if (tma) {
     CUtensorMap src_map, dst_map;
@@ -778,7 +944,9 @@ static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src
   if (tma && (variant < 0 || msg_op != FG_MSG_MUL || reduce_op != FG_REDUCE_SUM))
     return fail(FG_ERR_UNSUPPORTED, "FG_SDDMM_TMA_STAGING needs the multiply / sum operator pair, "
                 "feat_len a multiple of 32 and 16-byte aligned feature arrays");
-  const int warps = tma ? kTmWarps : kSdWarps;
+  const bool rowreg = (opt.flags & FG_SDDMM_ROW_REGISTERS) != 0 && variant >= 0 &&
+                      num_heads == 1 && !tma;
+  const int warps = tma ? kTmWarps : rowreg ? kRrWarps : kSdWarps;
   long long grid;
   long long tiles_per_warp = kSdTilesPerWarp;
   if (variant < 0) {
@@ -790,6 +958,7 @@ static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src
     if (opt.max_ctas > 0)
       tiles_per_warp = std::max<long long>(
           tiles_per_warp, (tiles + (long long)warps * opt.max_ctas - 1) / ((long long)warps * opt.max_ctas));
+    if (rowreg) tiles_per_warp = (tiles_per_warp + kRrTiles - 1) / kRrTiles * kRrTiles;
     if (tiles_per_warp >= INT32_MAX) return fail(FG_ERR_UNSUPPORTED, "edge count too large");
     const long long per_cta = (long long)warps * tiles_per_warp;
     grid = (tiles + per_cta - 1) / per_cta;
@@ -800,7 +969,7 @@ static int sddmm_launch(const int32_t* row, const int32_t* col, const float* src
 #define FG_SD_OPS(M, R)                                                                          \
   err = sddmm_launch_kernels<M, R>(variant, grid, (int)tiles_per_warp, programmatic, row, col,  \
                                    src, dst, out, nnz, n_rows, n_cols, feat_len, num_heads,     \
-                                   device, st, tma)
+                                   device, st, tma, rowreg)
   FG_DISPATCH_OPS(msg_op, reduce_op, FG_SD_OPS);
 #undef FG_SD_OPS
   FG_CUDA_TRY(err);
@@ -877,6 +1046,10 @@ extern "C" int fg_sddmm_coo_f32_host(const int32_t* row, const int32_t* col,
                                      int64_t n_cols, int32_t feat_len, int32_t num_heads,
                                      int32_t device, void* stream) {
   using namespace fg;
+  // the options of this call go to every piece's kernel (but for the programmatic launch:
+  // the pieces follow copies)
+  LaunchOptions opt = take_launch_options();
+  opt.flags &= ~FG_LAUNCH_PROGRAMMATIC;
   if (!src_host || !dst_host || !out_host || !src_stage || !dst_stage || !out_stage)
     return fail(FG_ERR_INVALID_ARGUMENT, "null host or staging buffer");
   if (nnz < 0 || n_rows < 0 || n_cols < 0 || feat_len <= 0 || num_heads <= 0)
@@ -902,6 +1075,7 @@ extern "C" int fg_sddmm_coo_f32_host(const int32_t* row, const int32_t* col,
   for (int k = 0; k < pieces && rc == FG_OK && err == cudaSuccess; ++k) {
     const int64_t e0 = nnz * k / pieces, e1 = nnz * (k + 1) / pieces;
     if (e1 == e0) continue;
+    if (opt.flags || opt.max_ctas) fg_next_launch_options(opt.flags, opt.max_ctas);
     rc = fg_sddmm_coo_f32(row + e0, col + e0, src_stage, dst_stage, out_stage + e0 * num_heads,
                           e1 - e0, n_rows, n_cols, feat_len, num_heads, device, stream);
     if (rc != FG_OK) break;
@@ -939,6 +1113,8 @@ extern "C" int fg_sddmm_coo_f32_push(const int32_t* row, const int32_t* col, con
   if (n_peers == 0 || nnz <= 0)
     return fg_sddmm_coo_f32(row, col, src, dst, out, nnz, n_rows, n_cols, feat_len, num_heads,
                             device, stream);
+  LaunchOptions opt = take_launch_options();  // handed to every piece's kernel
+  opt.flags &= ~FG_LAUNCH_PROGRAMMATIC;
   if (!out) return fail(FG_ERR_INVALID_ARGUMENT, "null device pointer");
   OutPtrs peers;
   peers.n = n_peers;
@@ -964,6 +1140,7 @@ extern "C" int fg_sddmm_coo_f32_push(const int32_t* row, const int32_t* col, con
     const int64_t e0 = std::min<int64_t>(nnz, tiles * k / pieces * 32);
     const int64_t e1 = std::min<int64_t>(nnz, tiles * (k + 1) / pieces * 32);
     if (e1 <= e0) continue;
+    if (opt.flags || opt.max_ctas) fg_next_launch_options(opt.flags, opt.max_ctas);
     const int rc = fg_sddmm_coo_f32(row + e0, col + e0, src, dst, out + e0 * num_heads, e1 - e0,
                                     n_rows, n_cols, feat_len, num_heads, device, stream);
     if (rc != FG_OK) return rc;

@@ -95,6 +95,28 @@ class SDDMMbase(object):
         _lib.load()
         self._spec, self._func = out, sched
         self.out_tvm = zeros(out.shape, out.dtype, self._ctx)
+        # one head over a list whose runs of 32 consecutive edges nearly all share a row:
+        # the kernel that keeps the dst operand in registers (FG_SDDMM_ROW_REGISTERS)
+        flags = getattr(self, "default_launch_flags", 0) & ~_lib.SDDMM_ROW_REGISTERS
+        if out.attrs["num_heads"] == 1 and out.attrs["feat_len"] % 32 == 0 \
+                and self._single_row_tile_share() >= 0.75:
+            flags |= _lib.SDDMM_ROW_REGISTERS
+        self.default_launch_flags = flags
+
+    def _single_row_tile_share(self):
+        """Share of the 32-edge tiles of the edge list whose edges all have one row index
+        (computed once per module, on the host)."""
+        if getattr(self, "_tile_share", None) is None:
+            rows = self._adj_row_indices
+            full = (rows.shape[0] // 32) * 32
+            if rows.dtype != np.int32 or full == 0:
+                self._tile_share = 0.0
+            else:
+                t = rows[:full].reshape(-1, 32)
+                self._tile_share = float((t[:, 0] == t[:, 31]).mean()
+                                         if bool((np.diff(rows) >= 0).all())
+                                         else (t == t[:, :1]).all(axis=1).mean())
+        return self._tile_share
 
     def lower_to_ir(self, input_placeholders, compute_args, schedule_args):
         """Debug text of the launch ``build`` would choose (sddmm.py:94-113)."""
@@ -188,7 +210,10 @@ class SDDMMbase(object):
         ``self.out_tvm``, the same array every call (sddmm.py:115-129).  ``launch_flags`` /
         ``max_ctas`` (additions): fg_next_launch_options for this call."""
         src, dst = self._checked_inputs(input_tvm_ndarrays)
-        self._launch(src, dst, launch_flags | getattr(self, "default_launch_flags", 0), max_ctas)
+        flags = launch_flags | getattr(self, "default_launch_flags", 0)
+        if flags & _lib.SDDMM_TMA_STAGING:
+            flags &= ~_lib.SDDMM_ROW_REGISTERS
+        self._launch(src, dst, flags, max_ctas)
         return self.out_tvm
 
     def measure_average_time(self, input_tvm_ndarrays, num_runs):
@@ -216,6 +241,8 @@ class SDDMMbase(object):
             self._stage = (torch.empty(sp_.shape, dtype=torch.float32, device=dev),
                            torch.empty(dp_.shape, dtype=torch.float32, device=dev))
         a = self._spec.attrs
+        if getattr(self, "default_launch_flags", 0):
+            _lib.check(_lib.load().fg_next_launch_options(self.default_launch_flags, 0))
         _lib.check(_lib.load().fg_sddmm_coo_f32_host(
             ptr(self._adj_row_indices_tvm.torch), ptr(self._adj_col_indices_tvm.torch),
             ptr(src_host), ptr(dst_host), ptr(out_host), ptr(self._stage[0]),

@@ -81,6 +81,14 @@ const char* fg_version(void);
  *   bit for bit.  Measured slower on B200 for 128-byte segments (3.57 against 2.82 ms at
  *   feat_len 64 on 114.6 M edges: the TMA unit takes about 16 cycles per four-row gather),
  *   so it is not the default.
+ * FG_SDDMM_ROW_REGISTERS (SDDMM, one head, feat_len a multiple of 32; a hint, ignored
+ *   where it does not apply): the kernel that keeps the dst operand in registers
+ *   (sddmm_rowreg_kernel) -- faster when nearly every run of 32 consecutive edges shares
+ *   one row index, as in a row-sorted list of a graph with long rows (2.64 against 2.82
+ *   ms at feat_len 64, 25.1 against 29.1 at 512, on 114.6 M edges); a tile that crosses
+ *   a row boundary reads its dst segments from global memory, so lists of short rows are
+ *   better served without it.  Same results bit for bit.  The Python module sets it by
+ *   itself from the edge list (module/sddmm.py).
  * The reference has no counterpart (one kernel, one stream). */
 enum fg_launch_flags {
   FG_LAUNCH_PROGRAMMATIC = 1,
@@ -88,7 +96,8 @@ enum fg_launch_flags {
   FG_SPMM_SKIP_GIANT_ROWS = 4,
   FG_SDDMM_TMA_STAGING = 8,
   FG_SPMM_LONG_ROWS_ONLY = 16,
-  FG_SPMM_SKIP_LONG_ROWS = 32
+  FG_SPMM_SKIP_LONG_ROWS = 32,
+  FG_SDDMM_ROW_REGISTERS = 64
 };
 int fg_next_launch_options(int32_t flags, int32_t max_ctas);
 

@@ -80,7 +80,7 @@ def test_spmm_in_two_phases_and_bounded_sddmm_grids(oracle):
                     launch_flags=_lib.LAUNCH_PROGRAMMATIC, max_ctas=max_ctas).asnumpy()
         assert np.array_equal(bits(want), bits(out)), max_ctas
     lib = _lib.load()
-    assert lib.fg_next_launch_options(64, 0) == 1 and lib.fg_next_launch_options(6, 0) == 1
+    assert lib.fg_next_launch_options(1 << 20, 0) == 1 and lib.fg_next_launch_options(6, 0) == 1
     assert lib.fg_next_launch_options(16 | 32, 0) == 1 and lib.fg_next_launch_options(2 | 32, 0) == 1
     assert lib.fg_next_launch_options(0, -1) == 1
     assert lib.fg_next_launch_options(1, 5) == 0 and lib.fg_next_launch_options(0, 0) == 0

@@ -333,3 +333,47 @@ def test_tma_staging_refuses_what_it_does_not_cover():
     m.build([te.placeholder(src.shape), te.placeholder(dst.shape)], {}, {"num_cuda_blocks": 64})
     with pytest.raises(_lib.FeatGraphError):        # feat_len 48 runs the generic kernel
         m.run([nd.array(src, m.ctx), nd.array(dst, m.ctx)], launch_flags=_lib.SDDMM_TMA_STAGING)
+
+
+@pytest.mark.parametrize("feat_len", [32, 64, 256])
+@pytest.mark.parametrize("ops", [("mul", "sum"), ("sub", "max")])
+def test_row_register_kernel_is_bit_identical(oracle, feat_len, ops):
+    # the kernel that keeps the dst operand in registers, forced by its launch flag: long rows
+    # (tiles inside one run of equal rows), short rows (every tile crosses row boundaries, dst
+    # read from global memory), a shuffled list, a ragged last tile and a last group of tiles
+    # that is not whole
+    long_rows = random_csr(40, 3000, 0.5, seed=101, empty_rows=(3,)).tocoo()
+    short_rows = random_csr(3000, 500, 0.01, seed=102).tocoo()
+    for adj, shuffle in ((long_rows, False), (short_rows, False), (long_rows, True)):
+        row, col = adj.row.astype(np.int32), adj.col.astype(np.int32)
+        if shuffle:
+            order = np.random.RandomState(103).permutation(row.shape[0])
+            row, col = row[order], col[order]
+        coo = sp.coo_matrix((np.ones(row.shape[0], np.float32), (row, col)), shape=adj.shape)
+        src = features((adj.shape[1], feat_len), seed=104)
+        dst = features((adj.shape[0], feat_len), seed=105)
+        m = VanillaSDDMMcuda(coo)
+        m.build([te.placeholder(src.shape), te.placeholder(dst.shape)],
+                {"msg_op": ops[0], "reduce_op": ops[1]}, {})
+        chosen = bool(m.default_launch_flags & _lib.SDDMM_ROW_REGISTERS)
+        assert chosen == (adj is long_rows and not shuffle)     # the module's own choice
+        for force in (0, _lib.SDDMM_ROW_REGISTERS):
+            m.default_launch_flags = force
+            m.out_tvm.torch.fill_(float("nan"))
+            y = m.run([nd.array(src, m.ctx), nd.array(dst, m.ctx)]).asnumpy()
+            want = oracle.gsddmm_coo_f32(row, col, src, dst, 1, ops[0], ops[1])
+            assert np.array_equal(bits(want.reshape(y.shape)), bits(y)), (force, shuffle)
+
+
+def test_row_register_hint_is_ignored_where_it_does_not_apply(oracle):
+    adj = random_csr(60, 70, 0.2, seed=106).tocoo()
+    for shape in ((48,), (4, 16)):                    # generic kernel; several heads
+        src, dst = features((70,) + shape, seed=107), features((60,) + shape, seed=108)
+        m = VanillaSDDMMcuda(adj)
+        m.build([te.placeholder(src.shape), te.placeholder(dst.shape)], {}, {"num_cuda_blocks": 64})
+        assert not m.default_launch_flags & _lib.SDDMM_ROW_REGISTERS
+        y = m.run([nd.array(src, m.ctx), nd.array(dst, m.ctx)],
+                  launch_flags=_lib.SDDMM_ROW_REGISTERS).asnumpy()
+        heads = shape[0] if len(shape) == 2 else 1
+        want = oracle.sddmm_coo_f32(adj.row, adj.col, src.reshape(70, -1), dst.reshape(60, -1), heads)
+        assert np.array_equal(bits(want.reshape(y.shape)), bits(y))

@@ -41,7 +41,7 @@ NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload on one GPU.
 # STATIC figures from one ncu capture (they do not follow later kernel changes until the
 # capture is repeated); other sizes and world sizes report null.
-NCU_TRAFFIC_BYTES = {"spmm": 1493.0e6 + 55.7e6, "sddmm": 1427.8e6 + 447.1e6}
+NCU_TRAFFIC_BYTES = {"spmm": 1494.9e6 + 55.6e6, "sddmm": 1417.8e6 + 449.7e6}
 NCU_TRAFFIC_SOURCE = ("static: one ncu capture (dram__bytes_read.sum + dram__bytes_write.sum, 1 pass) "
                       "of the full-size 1-GPU workload, summarised in "
                       "profiles/bench_full_size_launch_list_and_dram.md; it does not follow later "

@@ -125,7 +125,13 @@ class SDDMMbase(object):
         buf = ctypes.create_string_buffer(2048)
         _lib.check(_lib.load().fg_sddmm_describe(out.shape[0], out.attrs["feat_len"],
                                                  out.attrs["num_heads"], buf, len(buf)))
-        return buf.value.decode() + " | hints: %r" % (sched.hints,)
+        text = buf.value.decode()
+        if out.attrs["num_heads"] == 1 and out.attrs["feat_len"] % 32 == 0:
+            share = self._single_row_tile_share()
+            text += (" | %.0f %% of the 32-edge tiles lie inside one run of equal rows: %s"
+                     % (100 * share, "sddmm_rowreg_kernel (dst operand in registers, "
+                        "FG_SDDMM_ROW_REGISTERS) instead" if share >= 0.75 else "tile kernel kept"))
+        return text + " | hints: %r" % (sched.hints,)
 
     def set_extra_outputs(self, device_pointers, push=False):
         """Also deliver every result to these device addresses (peer-mapped copies of this

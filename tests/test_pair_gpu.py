@@ -26,19 +26,22 @@ def test_pair_on_one_gpu_equals_the_plain_calls(oracle):
     spmm = ShardedSpMM(adj, 64, dev)
     sddmm = ShardedSDDMM(g.coo_rows(), g.indices, g.n_rows, g.n_cols, 64, dev)
     assert all(n > 0 for n in row_classes(spmm.module))    # giant rows exist: all phases run
-    pair = OverlappedPair(spmm, sddmm)
-    assert pair.chained
-    for _ in range(3):                                     # overlapping changes nothing
-        spmm.out.fill_(float("nan"))
-        sddmm.out.fill_(float("nan"))
-        y, out = pair.run(x, y2, x)
-    torch.cuda.synchronize()
     want_y = oracle.spmm_csr_f32(adj.indptr, adj.indices, adj.data, x.cpu().numpy())
     want_o = oracle.sddmm_coo_f32(g.coo_rows().cpu().numpy(), g.indices.cpu().numpy(),
                                   y2.cpu().numpy(), x.cpu().numpy(), parallel=True)
-    assert np.array_equal(bits(want_y), bits(y.cpu().numpy()))
-    assert np.array_equal(bits(want_o), bits(out.cpu().numpy()))
-    assert spmm.device_status() == 0
+    # "chain": the SpMM, then the SDDMM behind it; "split": the SpMM's long rows, the SDDMM,
+    # the SpMM's light rows
+    for order in ("chain", "split"):
+        pair = OverlappedPair(spmm, sddmm, order=order)
+        assert pair.chained
+        for _ in range(3):                                 # overlapping changes nothing
+            spmm.out.fill_(float("nan"))
+            sddmm.out.fill_(float("nan"))
+            y, out = pair.run(x, y2, x)
+        torch.cuda.synchronize()
+        assert np.array_equal(bits(want_y), bits(y.cpu().numpy())), order
+        assert np.array_equal(bits(want_o), bits(out.cpu().numpy())), order
+        assert spmm.device_status() == 0
 
 
 def test_spmm_in_two_phases_and_bounded_sddmm_grids(oracle):

@@ -119,3 +119,24 @@ def test_float64_adjacency_is_rejected_not_cast(monkeypatch):
     adj = sp.random(8, 8, density=0.5, format="csr", dtype=np.float64, random_state=0)
     with pytest.raises(TypeError, match="float32"):
         VanillaSpMMx86(adj)
+
+
+def test_single_row_tile_share_of_an_edge_list():
+    # the statistic the cuda module uses to choose the row-register SDDMM kernel: the share
+    # of 32-edge tiles whose edges all have one row index (host side, so it runs here)
+    import scipy.sparse as sp
+    from featgraph_b200.module import VanillaSDDMMx86
+    rows = np.repeat(np.arange(10, dtype=np.int32), 320)           # 10 rows of 320 edges
+    cols = np.tile(np.arange(320, dtype=np.int32), 10)
+    coo = sp.coo_matrix((np.ones(3200, np.float32), (rows, cols)), shape=(10, 320))
+    assert VanillaSDDMMx86(coo)._single_row_tile_share() == 1.0
+    short = sp.coo_matrix((np.ones(3200, np.float32),
+                           (np.arange(3200, dtype=np.int32) // 4, cols)), shape=(800, 320))
+    assert VanillaSDDMMx86(short)._single_row_tile_share() == 0.0
+    order = np.random.RandomState(0).permutation(3200)             # unsorted: the general test
+    shuffled = sp.coo_matrix((np.ones(3200, np.float32), (rows[order], cols[order])),
+                             shape=(10, 320))
+    assert VanillaSDDMMx86(shuffled)._single_row_tile_share() < 0.05
+    tiny = sp.coo_matrix((np.ones(5, np.float32), (np.zeros(5, np.int32), np.arange(5, dtype=np.int32))),
+                         shape=(1, 5))
+    assert VanillaSDDMMx86(tiny)._single_row_tile_share() == 0.0   # no whole tile

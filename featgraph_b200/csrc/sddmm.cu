@@ -16,6 +16,11 @@
 // same row (the normal case for a row-sorted COO list) stage dst[row] once per
 // run and read it back as a broadcast.
 //
+// sddmm_rowreg_kernel: one head over a list with long runs of equal rows -- the dst
+// operand stays in registers across four tiles (chosen by a launch hint).
+// sddmm_tma_kernel: the tile kernel's arithmetic with the gathers done by TMA tile::gather4
+// copies (a launch option; slower on B200 for 128-byte segments).
+//
 // sddmm_generic_kernel: any shape / alignment, one thread per (edge, head).
 #include <cuda.h>  // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only; no libcuda link)
 

@@ -29,8 +29,12 @@
 //       whole call -- its sum is one dependent chain.
 //   * anything the vector paths cannot take (feat_len not a multiple of 32,
 //     unaligned pointers) -> spmm_generic_kernel, one warp per row.
+// With feat_len wider than the slab of X that stays in L2, that trio runs once per slab,
+// one trio after the other.
 // Every kernel is a template over a message operator and a reducer (common.cuh); multiply
 // with sum is the reference's SpMM, the other pairs are the generalised form.
+// At the end of the file: SpMM over the reference's column-blocked (DDS) form, as one CSR
+// call per column block whose stores add to the output.
 #include <algorithm>
 #include <cstring>
 #include <vector>
